@@ -1,0 +1,105 @@
+"""ctypes binding of ``libb200sort.so`` (the C ABI declared in ``include/b200sort.h``).
+
+There is no fallback: if the CUDA library is missing or a symbol is absent the import of the
+binding raises, and every call that returns a non-zero status raises ``B2SError``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(_HERE, "csrc")
+LIB_PATH = os.path.join(CSRC, "libb200sort.so")
+HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "b200sort.h")
+
+# b2s_dtype_t
+DTYPE_CODE = {
+    np.dtype(np.bool_): 1, np.dtype(np.int8): 2, np.dtype(np.int16): 3, np.dtype(np.int32): 4,
+    np.dtype(np.int64): 5, np.dtype(np.uint8): 6, np.dtype(np.uint16): 7, np.dtype(np.uint32): 8,
+    np.dtype(np.uint64): 9, np.dtype(np.float16): 10, np.dtype(np.float32): 11,
+    np.dtype(np.float64): 12, np.dtype(np.complex64): 13, np.dtype(np.complex128): 14,
+}
+
+B2S_OK = 0
+STATUS_NAMES = {0: "B2S_OK", 1: "B2S_ERR_INVALID_ARG", 2: "B2S_ERR_CUDA", 3: "B2S_ERR_NCCL",
+                4: "B2S_ERR_WORKSPACE", 5: "B2S_ERR_TIMEOUT", 6: "B2S_ERR_UNSUPPORTED"}
+
+
+class B2SError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = STATUS_NAMES.get(status, str(status))
+        try:
+            msg += ": " + lib().b2s_status_string(status).decode()
+        except Exception:  # pragma: no cover
+            pass
+        super().__init__(f"{where} failed with {msg}")
+
+
+def build_native(jobs: int = 8, force: bool = False) -> str:
+    """Compiles the CUDA library in-tree for sm_100a (``csrc/Makefile``)."""
+    env = dict(os.environ)
+    nccl_inc, nccl_lib = nccl_paths()
+    if nccl_inc:
+        env["NCCL_INC"] = nccl_inc
+        env["NCCL_LIB"] = nccl_lib
+    if force:
+        subprocess.run(["make", "-C", CSRC, "clean"], check=True, env=env, stdout=subprocess.DEVNULL)
+    subprocess.run(["make", "-C", CSRC, f"-j{jobs}", "-s"], check=True, env=env)
+    return LIB_PATH
+
+
+def nccl_paths():
+    """Include and library directories of the NCCL that torch itself loads."""
+    try:
+        import nvidia.nccl as _n  # type: ignore
+        root = list(_n.__path__)[0]
+        inc, libdir = os.path.join(root, "include"), os.path.join(root, "lib")
+        if os.path.exists(os.path.join(inc, "nccl.h")):
+            return inc, libdir
+    except Exception:
+        pass
+    if os.path.exists("/usr/include/nccl.h"):
+        return "/usr/include", "/usr/lib/x86_64-linux-gnu"
+    return None, None
+
+
+_lib = None
+
+_P, _SZ, _I, _I64 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int64
+
+# name -> (restype, argtypes); must list every function include/b200sort.h declares
+SIGNATURES = {
+    "b2s_status_string": (ctypes.c_char_p, [_I]),
+    "b2s_version": (_I, []),
+    "b2s_workspace_bytes": (_I, [_I, _SZ, _SZ, _I, ctypes.POINTER(_SZ)]),
+    "b2s_local_sort": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _I, _I, _P, _SZ, _P]),
+    "b2s_check_status": (_I, [_P, _P]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(there is no CPU or library fallback for the sort kernels)")
+        # torch loads the CUDA runtime and NCCL this library links against
+        import torch  # noqa: F401
+        handle = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status: int, where: str) -> None:
+    if status != B2S_OK:
+        raise B2SError(status, where)

@@ -1,0 +1,116 @@
+"""Host-side dispatch of the SORT task: axis handling and task construction.
+
+Mirrors the routing of ``cupynumeric/_thunk/_sort.py:37-136`` (same function names and
+argument meaning) on top of device-resident tiles instead of Legate stores:
+
+* ``sort_deferred``  0-D / ``axis=None`` / last-axis / other-axis routing   (ref ``:110-136``)
+* ``sort_flattened`` ``axis=None`` on an N-D array: sort the C-order flattening (ref ``:37-47``)
+* ``sort_swapped``   other axes: swap to last, dense copy, sort, swap back   (ref ``:50-76``)
+* ``sort_task``      one point task per process on its tile                  (ref ``:79-107``)
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+from numpy.exceptions import AxisError
+from numpy.lib.array_utils import normalize_axis_index
+
+from .. import _lib
+from ..runtime import runtime
+from .deferred import DeferredArray, create_deferred_thunk, to_numpy_dtype
+
+
+def local_sort_tile(tile: torch.Tensor, argsort: bool, stable: bool, index_offset: int = 0,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Runs the point task body on one dense row-major tile: sorts along the last axis.
+
+    This is the call the reference's ``SortImplBody<GPU>`` makes into ``local_sort``
+    (``src/cupynumeric/sort/sort.cu:1881-1891``), here into ``b2s_local_sort``.
+    """
+    lib = _lib.lib()
+    assert tile.is_cuda and tile.is_contiguous()
+    code = _lib.DTYPE_CODE[to_numpy_dtype(tile.dtype)]
+    volume = tile.numel()
+    segment = tile.shape[-1] if tile.ndim else 1
+    if out is None:
+        out = torch.empty(tile.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
+    if volume == 0:
+        return out
+    need = ctypes.c_size_t(0)
+    _lib.check(lib.b2s_workspace_bytes(code, volume, segment, int(argsort), ctypes.byref(need)),
+               "b2s_workspace_bytes")
+    ws = runtime.workspace(need.value)
+    st = lib.b2s_local_sort(code, tile.data_ptr(), None if argsort else out.data_ptr(),
+                            out.data_ptr() if argsort else None, volume, segment, int(index_offset),
+                            int(tile.ndim == 1), int(stable), ws.data_ptr(), ws.numel(),
+                            runtime.stream_handle())
+    _lib.check(st, "b2s_local_sort")
+    return out
+
+
+def sort_flattened(output: DeferredArray, input: DeferredArray, argsort: bool, stable: bool) -> None:
+    flat = input.reshape((input.size,), order="C")
+    result = create_deferred_thunk(flat.shape, dtype=output.dtype)
+    sort_deferred(result, flat, argsort, stable=stable)
+    output.base = result.base
+
+
+def sort_swapped(output: DeferredArray, input: DeferredArray, argsort: bool, sort_axis: int,
+                 stable: bool) -> None:
+    sort_axis = normalize_axis_index(sort_axis, input.ndim)
+    last = input.ndim - 1
+    if runtime.num_procs > 1 and sort_axis == 0:
+        # the sort axis is the tiled axis: needs the N-D sample sort with rebalancing
+        # (src/cupynumeric/sort/sort.cu:799-1261), which this build does not have yet
+        raise NotImplementedError("sorting along the axis that is split over processes")
+    moved = create_deferred_thunk(input.swapaxes(sort_axis, last).shape, dtype=input.dtype)
+    moved.copy(input.swapaxes(sort_axis, last), deep=True)
+    if argsort:
+        result = create_deferred_thunk(moved.shape, dtype=output.dtype)
+        sort_deferred(result, moved, argsort, stable=stable)
+        output.base = result.swapaxes(last, sort_axis).base
+    else:
+        sort_deferred(moved, moved, argsort, stable=stable)
+        output.base = moved.swapaxes(last, sort_axis).base
+
+
+def sort_task(output: DeferredArray, input: DeferredArray, argsort: bool, stable: bool) -> None:
+    """One point task per process on its tile; the tile's last axis is the sort axis.
+
+    A 1-D array held by several processes gets an "unbound" output: each process ends up with
+    however many elements fall between its splitters (ref ``:87,99-103``); N-D arrays are tiled
+    by rows, so every segment is local and no exchange happens (the reference reaches the same
+    state: ``need_distributed_sort == false``, ``src/cupynumeric/sort/sort.cu:1825``).
+    """
+    tile = input.base if input.base.is_contiguous() else input.base.contiguous()
+    uses_unbound_output = runtime.num_procs > 1 and input.ndim == 1
+    if uses_unbound_output:
+        from .._dist import dist_sort_1d
+
+        output.base, output.global_lo = dist_sort_1d(tile, argsort, input.global_lo)
+        return
+    # write straight into the output's memory when it is already there (in-place ndarray.sort)
+    out = output.base if (not argsort and output.base is not None and output.base.is_contiguous()
+                          and output.base.shape == tile.shape and output.base.dtype == tile.dtype) else None
+    output.base = local_sort_tile(tile, argsort, stable,
+                                  index_offset=input.global_lo if input.ndim == 1 else 0, out=out)
+    output.global_lo = input.global_lo
+
+
+def sort_deferred(output: DeferredArray, input: DeferredArray, argsort: bool, axis: int | None = -1,
+                  stable: bool = False) -> None:
+    if input.ndim == 0:
+        if axis is not None:
+            raise AxisError(axis, input.ndim)
+        output.base = input.base
+        return
+    if axis is None and input.ndim > 1:
+        sort_flattened(output, input, argsort, stable)
+        return
+    computed_axis = 0 if axis is None else normalize_axis_index(axis, input.ndim)
+    if computed_axis == input.ndim - 1:
+        sort_task(output, input, argsort, stable)
+    else:
+        sort_swapped(output, input, argsort, computed_axis, stable)

@@ -1,0 +1,97 @@
+"""Device-resident array thunk: the part of the reference's ``DeferredArray``
+(``cupynumeric/_thunk/deferred.py:287``) that the SORT path touches.
+
+``base`` is this process's dense, row-major tile of the global array (the whole array when one
+process runs).  With several processes the global array is tiled along axis 0 in rank order,
+which is how Legate tiles the stores of this task for the shapes in scope: 1-D arrays into
+contiguous ranges, N-D arrays into row blocks.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..runtime import runtime
+
+_NP2TORCH = {
+    np.dtype(np.bool_): torch.bool, np.dtype(np.int8): torch.int8, np.dtype(np.int16): torch.int16,
+    np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64, np.dtype(np.uint8): torch.uint8,
+    np.dtype(np.uint16): torch.uint16, np.dtype(np.uint32): torch.uint32,
+    np.dtype(np.uint64): torch.uint64, np.dtype(np.float16): torch.float16,
+    np.dtype(np.float32): torch.float32, np.dtype(np.float64): torch.float64,
+    np.dtype(np.complex64): torch.complex64, np.dtype(np.complex128): torch.complex128,
+}
+_TORCH2NP = {v: k for k, v in _NP2TORCH.items()}
+
+
+def to_torch_dtype(dt: Any) -> torch.dtype:
+    try:
+        return _NP2TORCH[np.dtype(dt)]
+    except (KeyError, TypeError):
+        # same failure mode as the reference's store conversion (cupynumeric/runtime.py:345-348)
+        raise TypeError(f"cuPyNumeric does not support dtype={dt}")
+
+
+def to_numpy_dtype(dt: torch.dtype) -> np.dtype:
+    return _TORCH2NP[dt]
+
+
+class DeferredArray:
+    def __init__(self, base: torch.Tensor | None, dtype: np.dtype | None = None,
+                 shape: tuple[int, ...] | None = None, global_lo: int = 0) -> None:
+        self.base = base
+        self._dtype = np.dtype(dtype) if dtype is not None else to_numpy_dtype(base.dtype)
+        self._shape = tuple(shape) if shape is not None else tuple(base.shape)
+        # position of this tile along axis 0 of the global array (1-D: first global index held)
+        self.global_lo = int(global_lo)
+
+    # ---- geometry ----
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return tuple(self.base.shape) if self.base is not None else self._shape
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    @property
+    def size(self) -> int:
+        return int(np.prod(self.shape, dtype=np.int64)) if self.ndim else 1
+
+    @property
+    def dtype(self) -> np.dtype:
+        return self._dtype
+
+    # ---- the views the sort dispatch needs ----
+    def reshape(self, newshape: tuple[int, ...], order: str = "C") -> "DeferredArray":
+        return DeferredArray(self.base.contiguous().reshape(newshape), global_lo=self.global_lo)
+
+    def swapaxes(self, axis1: int, axis2: int) -> "DeferredArray":
+        return DeferredArray(self.base.swapaxes(axis1, axis2), global_lo=self.global_lo)
+
+    def copy(self, rhs: "DeferredArray", deep: bool = True) -> None:
+        """Fills this thunk with a dense row-major copy of ``rhs``."""
+        self.base = rhs.base.contiguous() if not deep else rhs.base.clone(memory_format=torch.contiguous_format)
+
+    # ---- SORT ----
+    def sort(self, rhs: "DeferredArray", argsort: bool = False, axis: int | None = -1,
+             kind: str = "quicksort", order: Any = None) -> None:
+        """Same checks, in the same order, as ``DeferredArray.sort``
+        (``cupynumeric/_thunk/deferred.py:5453-5474``): only ``kind == "stable"`` requests a
+        stable sort; ``order`` is not supported; an out-of-range axis is a ``ValueError``."""
+        from ._sort import sort_deferred
+
+        stable = kind == "stable"
+        if order is not None:
+            raise NotImplementedError(
+                "cuPyNumeric does not support sorting with 'order' as ndarray only supports numeric values")
+        if axis is not None and (axis >= rhs.ndim or axis < -rhs.ndim):
+            raise ValueError("invalid axis")
+        sort_deferred(self, rhs, argsort, axis, stable)
+
+
+def create_deferred_thunk(shape: tuple[int, ...], dtype: Any) -> DeferredArray:
+    """An output thunk whose device memory is attached by the task that fills it."""
+    return DeferredArray(None, dtype=np.dtype(dtype), shape=tuple(shape))

@@ -1,0 +1,174 @@
+// extern "C" entry points of the local sort (declared in include/b200sort.h).
+#include "../../include/b200sort.h"
+#include "b2s_launch.cuh"
+
+namespace b2s {
+
+struct DtypeInfo {
+  int kb;
+  int xf;
+};
+
+// Key width and ordering rule per element type; complex types are not radix keys.
+inline bool dtype_info(int dtype, DtypeInfo* o)
+{
+  switch (dtype) {
+    case B2S_BOOL: *o = {1, XF_UNSIGNED}; return true;
+    case B2S_INT8: *o = {1, XF_SIGNED}; return true;
+    case B2S_INT16: *o = {2, XF_SIGNED}; return true;
+    case B2S_INT32: *o = {4, XF_SIGNED}; return true;
+    case B2S_INT64: *o = {8, XF_SIGNED}; return true;
+    case B2S_UINT8: *o = {1, XF_UNSIGNED}; return true;
+    case B2S_UINT16: *o = {2, XF_UNSIGNED}; return true;
+    case B2S_UINT32: *o = {4, XF_UNSIGNED}; return true;
+    case B2S_UINT64: *o = {8, XF_UNSIGNED}; return true;
+    case B2S_FLOAT16: *o = {2, XF_FLOAT}; return true;
+    case B2S_FLOAT32: *o = {4, XF_FLOAT}; return true;
+    case B2S_FLOAT64: *o = {8, XF_FLOAT}; return true;
+    default: return false;
+  }
+}
+
+inline size_t radix_ws(int kb, size_t n, bool pairs)
+{
+  switch (kb) {
+    case 1: return radix_1d_layout<1>(n, pairs).total;
+    case 2: return radix_1d_layout<2>(n, pairs).total;
+    case 4: return radix_1d_layout<4>(n, pairs).total;
+    default: return radix_1d_layout<8>(n, pairs).total;
+  }
+}
+
+inline cudaError_t radix_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int n,
+                             int64_t off, unsigned char* ws, cudaStream_t s)
+{
+  switch (kb) {
+    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s);
+    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s);
+    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s);
+    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s);
+  }
+}
+
+inline cudaError_t seg_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int L,
+                           unsigned long long nseg, int64_t off, Ctrl* ctrl, cudaStream_t s)
+{
+  switch (kb) {
+    case 1: return launch_segsort<1>(xf, in, out, idx, L, nseg, off, ctrl, s);
+    case 2: return launch_segsort<2>(xf, in, out, idx, L, nseg, off, ctrl, s);
+    case 4: return launch_segsort<4>(xf, in, out, idx, L, nseg, off, ctrl, s);
+    default: return launch_segsort<8>(xf, in, out, idx, L, nseg, off, ctrl, s);
+  }
+}
+
+// Segments of one element: the output is the input, every index is index_offset.
+__global__ void unit_segment_kernel(const unsigned char* in, unsigned char* out, int64_t* idx, size_t volume,
+                                    int kb, int64_t index_offset)
+{
+  const size_t gthread = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t gstride = (size_t)gridDim.x * blockDim.x;
+  if (out != nullptr && out != in)
+    for (size_t i = gthread; i < volume * kb; i += gstride) out[i] = in[i];
+  if (idx != nullptr)
+    for (size_t i = gthread; i < volume; i += gstride) idx[i] = index_offset;
+}
+
+// Segments longer than the on-chip kernel takes are sorted one after the other by the 1-D path
+// while there are few of them.
+constexpr size_t MAX_LOOPED_SEGMENTS = 4096;
+
+}  // namespace b2s
+
+using namespace b2s;
+
+extern "C" {
+
+const char* b2s_status_string(int status)
+{
+  switch (status) {
+    case B2S_OK: return "ok";
+    case B2S_ERR_INVALID_ARG: return "invalid argument";
+    case B2S_ERR_CUDA: return "CUDA error";
+    case B2S_ERR_NCCL: return "NCCL error";
+    case B2S_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case B2S_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case B2S_ERR_UNSUPPORTED: return "unsupported dtype or shape";
+    default: return "unknown status";
+  }
+}
+
+int b2s_version(void) { return 100; }
+
+int b2s_workspace_bytes(int dtype, size_t volume, size_t segment, int argsort, size_t* bytes)
+{
+  DtypeInfo di;
+  if (bytes == nullptr) return B2S_ERR_INVALID_ARG;
+  if (!dtype_info(dtype, &di)) return B2S_ERR_UNSUPPORTED;
+  if (volume > 0 && (segment == 0 || volume % segment != 0)) return B2S_ERR_INVALID_ARG;
+  size_t need = align_up(sizeof(Ctrl), 256);
+  if (volume > 0 && segment > SEG_CAP) {
+    if (segment >= MAX_N_1D) return B2S_ERR_UNSUPPORTED;
+    need = radix_ws(di.kb, segment, argsort != 0);
+  }
+  *bytes = need;
+  return B2S_OK;
+}
+
+int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t volume,
+                   size_t segment, int64_t index_offset, int ndim_is_1, int stable, void* ws, size_t ws_bytes,
+                   void* cuda_stream)
+{
+  (void)stable;  // always stable
+  DtypeInfo di;
+  if (!dtype_info(dtype, &di)) return B2S_ERR_UNSUPPORTED;
+  if (volume == 0) return B2S_OK;
+  if (keys_in == nullptr || (keys_out == nullptr && idx_out == nullptr)) return B2S_ERR_INVALID_ARG;
+  if (segment == 0 || volume % segment != 0) return B2S_ERR_INVALID_ARG;
+  const size_t nseg = volume / segment;
+  if (ndim_is_1 && nseg != 1) return B2S_ERR_INVALID_ARG;
+  size_t need = 0;
+  int rc      = b2s_workspace_bytes(dtype, volume, segment, idx_out != nullptr, &need);
+  if (rc != B2S_OK) return rc;
+  if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  Ctrl* ctrl          = static_cast<Ctrl*>(ws);
+  cudaError_t e;
+
+  if (segment <= SEG_CAP) {
+    e = cudaMemsetAsync(ctrl, 0, sizeof(Ctrl), stream);
+    if (e != cudaSuccess) return B2S_ERR_CUDA;
+    if (segment == 1) {
+      size_t grid = (volume + 4095) / 4096;
+      if (grid > 148 * 8) grid = 148 * 8;
+      unit_segment_kernel<<<(unsigned int)grid, 256, 0, stream>>>(static_cast<const unsigned char*>(keys_in),
+                                                                 static_cast<unsigned char*>(keys_out), idx_out,
+                                                                 volume, di.kb, index_offset);
+      return cudaGetLastError() == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
+    }
+    e = seg_any(di.kb, di.xf, keys_in, keys_out, idx_out, (unsigned int)segment, nseg, index_offset, ctrl, stream);
+    return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
+  }
+
+  if (nseg > MAX_LOOPED_SEGMENTS) return B2S_ERR_UNSUPPORTED;
+  for (size_t s = 0; s < nseg; ++s) {
+    const unsigned char* in = static_cast<const unsigned char*>(keys_in) + s * segment * di.kb;
+    unsigned char* out = keys_out ? static_cast<unsigned char*>(keys_out) + s * segment * di.kb : nullptr;
+    int64_t* idx       = idx_out ? idx_out + s * segment : nullptr;
+    e = radix_any(di.kb, di.xf, in, out, idx, (unsigned int)segment, index_offset, static_cast<unsigned char*>(ws),
+                  stream);
+    if (e != cudaSuccess) return B2S_ERR_CUDA;
+  }
+  return B2S_OK;
+}
+
+int b2s_check_status(void* ws, void* cuda_stream)
+{
+  if (ws == nullptr) return B2S_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  unsigned int st     = 0;
+  if (cudaMemcpyAsync(&st, &static_cast<Ctrl*>(ws)->status, sizeof(st), cudaMemcpyDeviceToHost, stream) != cudaSuccess)
+    return B2S_ERR_CUDA;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return B2S_ERR_CUDA;
+  return (int)st;
+}
+}

@@ -1,0 +1,196 @@
+// Shared device/host definitions of the sm_100a SORT kernels: key types, the order-preserving
+// key transforms, PTX helpers (mbarrier, bulk async copy, relaxed global accesses) and the
+// control block that lives at the head of every workspace.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2s {
+
+// ---------------------------------------------------------------------------------------------
+// Key storage types: keys travel through every pass as their ORIGINAL bits; only the digit
+// extractor sees the transformed (order-preserving, unsigned) value.
+// ---------------------------------------------------------------------------------------------
+template <int KB> struct KeyOf;
+template <> struct KeyOf<1> { using type = uint8_t; };
+template <> struct KeyOf<2> { using type = uint16_t; };
+template <> struct KeyOf<4> { using type = uint32_t; };
+template <> struct KeyOf<8> { using type = uint64_t; };
+
+// Ordering rule of a dtype.
+enum : int {
+  XF_UNSIGNED = 0,  // bool, uintN
+  XF_SIGNED   = 1,  // intN: flip the sign bit
+  XF_FLOAT    = 2   // IEEE floats: -inf < .. < -0.0 == +0.0 < .. < +inf < every NaN
+};
+
+// Maps raw key bits to an unsigned integer whose natural order is the sort order.
+// Floats: every NaN (either sign, any payload) maps to all-ones so that NaNs come last and keep
+// their input order; -0.0 maps to the image of +0.0 so the two stay in input order.  The
+// reference's CPU variant compares with raw '<' (src/cupynumeric/sort/sort_cpu.inl:64-81),
+// under which -0.0 == +0.0; NumPy's sort, the reference tests' oracle, puts NaN last.
+template <int KB, int XF>
+__host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered(typename KeyOf<KB>::type raw)
+{
+  using K        = typename KeyOf<KB>::type;
+  constexpr K SB = (K)((K)1 << (8 * KB - 1));
+  if (XF == XF_UNSIGNED) {
+    return raw;
+  } else if (XF == XF_SIGNED) {
+    return (K)(raw ^ SB);
+  } else {
+    // exponent mask: all exponent bits set = inf/NaN
+    constexpr K EXP = (KB == 2) ? (K)0x7C00u : (KB == 4) ? (K)0x7F800000u : (K)0x7FF0000000000000ull;
+    const K mag     = (K)(raw & (K)~SB);
+    if (mag > EXP) { return (K)~(K)0; }           // NaN
+    if (mag == 0) { return SB; }                  // +0.0 and -0.0
+    return (raw & SB) ? (K)~raw : (K)(raw | SB);
+  }
+}
+
+template <int KB>
+__host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered_rt(typename KeyOf<KB>::type raw, int xf)
+{
+  if (xf == XF_UNSIGNED) return to_ordered<KB, XF_UNSIGNED>(raw);
+  if (xf == XF_SIGNED) return to_ordered<KB, XF_SIGNED>(raw);
+  if (KB >= 2) return to_ordered<(KB >= 2 ? KB : 2), XF_FLOAT>(raw);
+  return raw;
+}
+
+// Raw bit pattern whose ordered image is all-ones: pads partial tiles so that the padding
+// ranks after every real key of the tile.
+template <int KB>
+__host__ __device__ __forceinline__ typename KeyOf<KB>::type pad_raw(int xf)
+{
+  using K = typename KeyOf<KB>::type;
+  return xf == XF_UNSIGNED ? (K)~(K)0 : (K)((K)~(K)0 >> 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Control block at the start of a workspace (zeroed by one memset per sort call).
+// ---------------------------------------------------------------------------------------------
+constexpr int RADIX_BITS = 8;
+constexpr int RADIX      = 1 << RADIX_BITS;
+constexpr int MAX_PASSES = 8;
+
+struct PassDesc {
+  const void* src_keys;
+  void* dst_keys;          // nullptr: this pass does not write keys
+  const int64_t* src_idx;  // nullptr: indices are synthesised from the element position
+  int64_t* dst_idx;
+  int active;              // 0: the digit is constant over the whole array, pass is the identity
+  int pad_;
+};
+
+struct FixDesc {
+  const void* copy_src;  // non-null: copy copy_bytes from here to copy_dst
+  void* copy_dst;
+  unsigned long long copy_bytes;
+  int64_t* synth_idx;    // non-null: write index_offset + i
+  int pad_[2];
+};
+
+struct Ctrl {
+  unsigned int status;                  // 0 or a b2s_status_t, written by kernels
+  unsigned int abort;                   // set with status; every later wait gives up at once
+  unsigned int tile_counter[MAX_PASSES];
+  unsigned int pad_[6];
+  unsigned int hist[MAX_PASSES][RADIX]; // digit counts, then (after the scan kernel) exclusive bases
+  PassDesc pass[MAX_PASSES];
+  FixDesc fix;
+};
+
+constexpr unsigned int DEV_ERR_TIMEOUT = 5;  // == B2S_ERR_TIMEOUT
+
+// Upper bound on polls of any device-side wait; on overrun the kernel records DEV_ERR_TIMEOUT,
+// raises `abort`, publishes what its successors wait for and returns.
+constexpr unsigned int SPIN_LIMIT = 1u << 22;
+
+// ---------------------------------------------------------------------------------------------
+// PTX helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* p)
+{
+  unsigned int v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed(unsigned int* p, unsigned int v)
+{
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init()
+{
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+// Orders generic-proxy accesses to shared memory before later async-proxy (bulk copy) accesses.
+__device__ __forceinline__ void fence_proxy_async()
+{
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// Bulk asynchronous copy global -> shared (TMA engine, untiled form).  dst, src and bytes must
+// all be multiples of 16.  Completion is signalled on `bar` as transferred bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar)
+{
+  asm volatile(
+    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+      smem_u32(smem_dst)),
+    "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+    : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+{
+  uint32_t ok;
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t"
+    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+    "selp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(ok)
+    : "r"(smem_u32(bar)), "r"(parity)
+    : "memory");
+  return ok != 0;
+}
+// Bounded wait on an mbarrier phase. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
+{
+  for (unsigned int i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ unsigned int lanemask_lt()
+{
+  unsigned int m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
+}
+
+__device__ __forceinline__ void raise_timeout(Ctrl* ctrl)
+{
+  atomicMax(&ctrl->status, DEV_ERR_TIMEOUT);
+  atomicExch(&ctrl->abort, 1u);
+}
+
+template <int KB, int XF>
+__device__ __forceinline__ unsigned int digit_of(typename KeyOf<KB>::type raw, int shift)
+{
+  return (unsigned int)(to_ordered<KB, XF>(raw) >> shift) & (RADIX - 1);
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace b2s

@@ -1,0 +1,165 @@
+// Host-side launchers of the local sort kernels, templated on the key width so that each width
+// compiles in a translation unit of its own.
+#pragma once
+
+#include "b2s_radix.cuh"
+#include "b2s_segsort.cuh"
+
+namespace b2s {
+
+// Largest segment the on-chip segmented kernel takes.
+constexpr unsigned int SEG_CAP = 8192;
+
+// Tile shape of the onesweep pass per key width / payload.
+template <int KB, bool PAIRS> struct SweepCfg {
+  static constexpr int THREADS = (!PAIRS && KB <= 4) ? 512 : 256;
+  static constexpr int ITEMS   = 16;
+  static constexpr int TILE    = THREADS * ITEMS;
+};
+
+struct Radix1dLayout {
+  size_t off_lookback, off_keys[2], off_idx[2], total;
+  unsigned int tiles;
+};
+
+template <int KB>
+inline Radix1dLayout radix_1d_layout(size_t n, bool pairs)
+{
+  Radix1dLayout l{};
+  const unsigned int tile = pairs ? SweepCfg<KB, true>::TILE : SweepCfg<KB, false>::TILE;
+  l.tiles                 = (unsigned int)((n + tile - 1) / tile);
+  size_t off              = align_up(sizeof(Ctrl), 256);
+  l.off_lookback          = off;
+  off += align_up((size_t)KB * l.tiles * RADIX * sizeof(unsigned int), 256);
+  for (int i = 0; i < 2; ++i) {
+    l.off_keys[i] = off;
+    off += align_up(n * KB, 256);
+  }
+  for (int i = 0; i < 2; ++i) {
+    l.off_idx[i] = off;
+    if (pairs) off += align_up(n * 8, 256);
+  }
+  l.total = off;
+  return l;
+}
+
+template <int KB, int XF, bool PAIRS>
+inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned int tiles, unsigned int n,
+                                 int64_t index_offset, cudaStream_t stream)
+{
+  using C   = SweepCfg<KB, PAIRS>;
+  using S   = SweepSmem<KB, PAIRS, C::THREADS, C::ITEMS>;
+  auto kern = onesweep_kernel<KB, XF, PAIRS, C::THREADS, C::ITEMS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::BYTES);
+  if (e != cudaSuccess) return e;
+  for (int pass = 0; pass < KB; ++pass) {
+    kern<<<tiles, C::THREADS, S::BYTES, stream>>>(ctrl, lookback + (size_t)pass * tiles * RADIX, pass, n,
+                                                  index_offset);
+  }
+  return cudaGetLastError();
+}
+
+template <int KB, int XF>
+inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsigned int n,
+                               int64_t index_offset, unsigned char* ws, cudaStream_t stream)
+{
+  using K            = typename KeyOf<KB>::type;
+  const bool pairs   = idx_out != nullptr;
+  const auto lay     = radix_1d_layout<KB>(n, pairs);
+  Ctrl* ctrl         = reinterpret_cast<Ctrl*>(ws);
+  unsigned int* lb   = reinterpret_cast<unsigned int*>(ws + lay.off_lookback);
+  cudaError_t e      = cudaMemsetAsync(ws, 0, lay.off_keys[0], stream);  // control block + look-back table
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const unsigned int per_cta = HIST_THREADS * 16;
+  unsigned int hgrid         = (n + per_cta - 1) / per_cta;
+  if (hgrid > (unsigned int)sms * 4) hgrid = sms * 4;
+  hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl);
+  RouteArgs ra{};
+  ra.keys_in     = in;
+  ra.keys_out    = out;
+  ra.idx_out     = idx_out;
+  ra.tmp_keys[0] = ws + lay.off_keys[0];
+  ra.tmp_keys[1] = ws + lay.off_keys[1];
+  ra.tmp_idx[0]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[0]);
+  ra.tmp_idx[1]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[1]);
+  ra.n           = n;
+  ra.npass       = KB;
+  ra.key_bytes   = KB;
+  scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
+  e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, n, index_offset, stream)
+            : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, n, index_offset, stream);
+  if (e != cudaSuccess) return e;
+  unsigned int fgrid = (n + 256 * 16 - 1) / (256 * 16);
+  if (fgrid > (unsigned int)sms * 8) fgrid = sms * 8;
+  fixup_kernel<<<fgrid, 256, 0, stream>>>(ctrl, n, index_offset);
+  return cudaGetLastError();
+}
+
+// 1-D stable sort of n < 2^30 keys. `ws` must hold radix_1d_layout<KB>(n, idx_out != null).total bytes.
+template <int KB>
+cudaError_t launch_radix_1d(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,
+                            int64_t index_offset, unsigned char* ws, cudaStream_t stream);
+
+// Segments of seg_len <= SEG_CAP elements, sorted on chip. `ctrl` must be a zeroed control block.
+template <int KB>
+cudaError_t launch_segsort(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
+                           unsigned long long nseg, int64_t index_offset, Ctrl* ctrl, cudaStream_t stream);
+
+template <int KB, bool PAIRS, int THREADS, int ITEMS>
+inline cudaError_t segsort_cfg(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
+                               unsigned long long nseg, int64_t index_offset, Ctrl* ctrl, cudaStream_t stream)
+{
+  using K   = typename KeyOf<KB>::type;
+  using S   = SegSmem<KB, PAIRS, THREADS, ITEMS>;
+  auto kern = segsort_kernel<KB, PAIRS, THREADS, ITEMS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::BYTES);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int per_sm = 1;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, S::BYTES);
+  if (per_sm < 1) per_sm = 1;
+  unsigned long long grid = (unsigned long long)sms * per_sm;
+  if (grid > nseg) grid = nseg;
+  kern<<<(unsigned int)grid, THREADS, S::BYTES, stream>>>(static_cast<const K*>(in), static_cast<K*>(out),
+                                                           idx_out, seg_len, nseg, xf, index_offset, ctrl);
+  return cudaGetLastError();
+}
+
+template <int KB, bool PAIRS>
+inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
+                                 unsigned long long nseg, int64_t index_offset, Ctrl* ctrl, cudaStream_t stream)
+{
+  if (seg_len <= 128) return segsort_cfg<KB, PAIRS, 32, 4>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
+  if (seg_len <= 1024) return segsort_cfg<KB, PAIRS, 128, 8>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
+  if (seg_len <= 4096) return segsort_cfg<KB, PAIRS, 256, 16>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
+  return segsort_cfg<KB, PAIRS, 512, 16>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
+}
+
+#define B2S_INSTANTIATE_KEY_WIDTH(KB, HAS_FLOAT)                                                          \
+  template <>                                                                                             \
+  cudaError_t launch_radix_1d<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,    \
+                                  int64_t index_offset, unsigned char* ws, cudaStream_t stream)           \
+  {                                                                                                       \
+    if (xf == XF_UNSIGNED) return radix_1d_xf<KB, XF_UNSIGNED>(in, out, idx_out, n, index_offset, ws, stream); \
+    if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream); \
+    if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
+      return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream); \
+    return cudaErrorInvalidValue;                                                                         \
+  }                                                                                                       \
+  template <>                                                                                             \
+  cudaError_t launch_segsort<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len, \
+                                 unsigned long long nseg, int64_t index_offset, Ctrl* ctrl,               \
+                                 cudaStream_t stream)                                                     \
+  {                                                                                                       \
+    if (!HAS_FLOAT && xf == XF_FLOAT) return cudaErrorInvalidValue;                                       \
+    if (idx_out != nullptr)                                                                               \
+      return segsort_pairs<KB, true>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);    \
+    return segsort_pairs<KB, false>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);     \
+  }
+
+}  // namespace b2s
