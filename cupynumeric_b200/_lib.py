@@ -25,6 +25,8 @@ DTYPE_CODE = {
 }
 
 B2S_OK = 0
+# b2s_kernel_kind_t
+K_HIST, K_SCAN, K_SWEEP, K_FIXUP, K_SEGSORT, K_UNIT, K_DIST, K_MERGE = range(8)
 STATUS_NAMES = {0: "B2S_OK", 1: "B2S_ERR_INVALID_ARG", 2: "B2S_ERR_CUDA", 3: "B2S_ERR_NCCL",
                 4: "B2S_ERR_WORKSPACE", 5: "B2S_ERR_TIMEOUT", 6: "B2S_ERR_UNSUPPORTED"}
 
@@ -79,6 +81,9 @@ SIGNATURES = {
     "b2s_workspace_bytes": (_I, [_I, _SZ, _SZ, _I, ctypes.POINTER(_SZ)]),
     "b2s_local_sort": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _I, _I, _P, _SZ, _P]),
     "b2s_check_status": (_I, [_P, _P]),
+    "b2s_profile_enable": (_I, [_I]),
+    "b2s_profile_read": (_I, [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_ulonglong)]),
+    "b2s_launch_count": (ctypes.c_ulonglong, [_I]),
 }
 
 

@@ -140,6 +140,7 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
     if (segment == 1) {
       size_t grid = (volume + 4095) / 4096;
       if (grid > 148 * 8) grid = 148 * 8;
+      prof::Scope ps(prof::K_UNIT, stream);
       unit_segment_kernel<<<(unsigned int)grid, 256, 0, stream>>>(static_cast<const unsigned char*>(keys_in),
                                                                  static_cast<unsigned char*>(keys_out), idx_out,
                                                                  volume, di.kb, index_offset);

@@ -2,6 +2,7 @@
 // compiles in a translation unit of its own.
 #pragma once
 
+#include "b2s_prof.h"
 #include "b2s_radix.cuh"
 #include "b2s_segsort.cuh"
 
@@ -53,6 +54,7 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::BYTES);
   if (e != cudaSuccess) return e;
   for (int pass = 0; pass < KB; ++pass) {
+    prof::Scope ps(prof::K_SWEEP, stream);
     kern<<<tiles, C::THREADS, S::BYTES, stream>>>(ctrl, lookback + (size_t)pass * tiles * RADIX, pass, n,
                                                   index_offset);
   }
@@ -76,7 +78,10 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   const unsigned int per_cta = HIST_THREADS * 16;
   unsigned int hgrid         = (n + per_cta - 1) / per_cta;
   if (hgrid > (unsigned int)sms * 4) hgrid = sms * 4;
-  hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl);
+  {
+    prof::Scope ps(prof::K_HIST, stream);
+    hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl);
+  }
   RouteArgs ra{};
   ra.keys_in     = in;
   ra.keys_out    = out;
@@ -88,13 +93,19 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.n           = n;
   ra.npass       = KB;
   ra.key_bytes   = KB;
-  scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
+  {
+    prof::Scope ps(prof::K_SCAN, stream);
+    scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
+  }
   e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, n, index_offset, stream)
             : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, n, index_offset, stream);
   if (e != cudaSuccess) return e;
   unsigned int fgrid = (n + 256 * 16 - 1) / (256 * 16);
   if (fgrid > (unsigned int)sms * 8) fgrid = sms * 8;
-  fixup_kernel<<<fgrid, 256, 0, stream>>>(ctrl, n, index_offset);
+  {
+    prof::Scope ps(prof::K_FIXUP, stream);
+    fixup_kernel<<<fgrid, 256, 0, stream>>>(ctrl, n, index_offset);
+  }
   return cudaGetLastError();
 }
 
@@ -125,8 +136,11 @@ inline cudaError_t segsort_cfg(int xf, const void* in, void* out, int64_t* idx_o
   if (per_sm < 1) per_sm = 1;
   unsigned long long grid = (unsigned long long)sms * per_sm;
   if (grid > nseg) grid = nseg;
-  kern<<<(unsigned int)grid, THREADS, S::BYTES, stream>>>(static_cast<const K*>(in), static_cast<K*>(out),
-                                                           idx_out, seg_len, nseg, xf, index_offset, ctrl);
+  {
+    prof::Scope ps(prof::K_SEGSORT, stream);
+    kern<<<(unsigned int)grid, THREADS, S::BYTES, stream>>>(static_cast<const K*>(in), static_cast<K*>(out),
+                                                             idx_out, seg_len, nseg, xf, index_offset, ctrl);
+  }
   return cudaGetLastError();
 }
 

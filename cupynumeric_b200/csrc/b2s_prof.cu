@@ -1,0 +1,97 @@
+// Launch counters and optional per-kernel event timing (see include/b200sort.h:
+// b2s_profile_enable / b2s_profile_read / b2s_launch_count).  Process-wide and not
+// thread-safe by design: it is a measurement aid for single-threaded harnesses.
+#include <vector>
+
+#include "../../include/b200sort.h"
+#include "b2s_prof.h"
+
+namespace b2s {
+namespace prof {
+
+struct Rec {
+  int kind;
+  cudaEvent_t a, b;
+};
+static bool g_enabled = false;
+static std::vector<Rec> g_recs;           // event pairs in use since the last enable/reset
+static std::vector<cudaEvent_t> g_pool;   // spare events
+static unsigned long long g_launches[K_COUNT] = {};
+
+static cudaEvent_t take_event()
+{
+  cudaEvent_t e = nullptr;
+  if (!g_pool.empty()) {
+    e = g_pool.back();
+    g_pool.pop_back();
+  } else {
+    cudaEventCreate(&e);
+  }
+  return e;
+}
+
+void begin(int kind, cudaStream_t stream)
+{
+  ++g_launches[kind];
+  if (!g_enabled) return;
+  Rec r{kind, take_event(), take_event()};
+  cudaEventRecord(r.a, stream);
+  g_recs.push_back(r);
+}
+
+void end(int kind, cudaStream_t stream)
+{
+  (void)kind;
+  if (!g_enabled || g_recs.empty()) return;
+  cudaEventRecord(g_recs.back().b, stream);
+}
+
+static void recycle()
+{
+  for (auto& r : g_recs) {
+    g_pool.push_back(r.a);
+    g_pool.push_back(r.b);
+  }
+  g_recs.clear();
+}
+
+}  // namespace prof
+}  // namespace b2s
+
+using namespace b2s::prof;
+
+extern "C" {
+
+int b2s_profile_enable(int on)
+{
+  recycle();
+  g_enabled = on != 0;
+  return B2S_OK;
+}
+
+int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches)
+{
+  if (kind < 0 || kind >= K_COUNT) return B2S_ERR_INVALID_ARG;
+  double tot = 0;
+  unsigned long long cnt = 0;
+  for (auto& r : g_recs) {
+    if (r.kind != kind) continue;
+    if (cudaEventSynchronize(r.b) != cudaSuccess) return B2S_ERR_CUDA;
+    float ms = 0;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) != cudaSuccess) return B2S_ERR_CUDA;
+    tot += ms;
+    ++cnt;
+  }
+  if (total_ms) *total_ms = tot;
+  if (launches) *launches = cnt;
+  return B2S_OK;
+}
+
+unsigned long long b2s_launch_count(int kind)
+{
+  if (kind >= 0 && kind < K_COUNT) return g_launches[kind];
+  unsigned long long t = 0;
+  for (int k = 0; k < K_COUNT; ++k) t += g_launches[k];
+  return t;
+}
+}

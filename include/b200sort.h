@@ -96,6 +96,33 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
  * CUPYNUMERIC_CHECK_CUDA_STREAM (src/cupynumeric/cuda_help.h:291-302). */
 int b2s_check_status(void* ws, void* cuda_stream);
 
+/* ---- measurement aids (no counterpart in the reference, which relies on Legate's profiler,
+ * cupynumeric/_utils/profiling.py:33-73) ------------------------------------------------------ */
+
+/* Kernel families counted and timed separately. */
+typedef enum {
+  B2S_K_HIST    = 0, /* digit histograms */
+  B2S_K_SCAN    = 1, /* histogram scan + pass routing */
+  B2S_K_SWEEP   = 2, /* onesweep radix pass */
+  B2S_K_FIXUP   = 3, /* leftover copies / synthesised indices */
+  B2S_K_SEGSORT = 4, /* on-chip segmented sort */
+  B2S_K_UNIT    = 5, /* segments of one element */
+  B2S_K_DIST    = 6, /* sampling, splitter search and cut kernels of the distributed sort */
+  B2S_K_MERGE   = 7, /* k-way merge */
+  B2S_K_COUNT   = 8
+} b2s_kernel_kind_t;
+
+/* Switches per-launch CUDA-event timing on or off and forgets earlier records.  Process-wide,
+ * not thread-safe: meant for a single-threaded benchmark harness. */
+int b2s_profile_enable(int on);
+
+/* Sum of the event-timed durations (ms) and number of launches of one kernel family since
+ * b2s_profile_enable(1).  Waits for the recorded launches to finish. */
+int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches);
+
+/* Number of kernels of one family (or of all, kind < 0) this process has launched so far. */
+unsigned long long b2s_launch_count(int kind);
+
 #ifdef __cplusplus
 }
 #endif

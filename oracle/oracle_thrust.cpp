@@ -185,3 +185,6 @@ int oracle_sort(int dtype, void* keys, int64_t* idx, size_t volume, size_t segme
 
 int oracle_thrust_version(void) { return THRUST_VERSION; }
 }
+
+#include <omp.h>
+extern "C" int oracle_num_threads(void) { return omp_get_max_threads(); }

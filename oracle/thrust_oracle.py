@@ -43,6 +43,11 @@ def _load():
     return _lib
 
 
+def num_threads() -> int:
+    """Threads the OpenMP back-end will use (OMP_NUM_THREADS or all cores)."""
+    return int(_load().oracle_num_threads())
+
+
 def thrust_task_sort(keys: np.ndarray, segment: int, argsort: bool, index_offset: int = 0,
                      ndim_is_1: bool = True, stable: bool = True, backend: str = "host",
                      nan_mode: str | None = None):
