@@ -13,7 +13,8 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-LIB_PATH = os.path.join(CSRC, "libb200sort.so")
+# B2S_LIB_PATH selects another build of the same library (e.g. a tuning variant)
+LIB_PATH = os.environ.get("B2S_LIB_PATH") or os.path.join(CSRC, "libb200sort.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "b200sort.h")
 
 # b2s_dtype_t

@@ -151,22 +151,28 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
     "l"(__cvta_generic_to_global(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
     : "memory");
 }
+// One bounded attempt: the hardware may park the thread for up to `MBAR_SUSPEND_NS` before it
+// answers, so a waiting thread does not spend issue slots polling.
+constexpr uint32_t MBAR_SUSPEND_NS = 20000;
+constexpr unsigned int MBAR_TRIES  = 1u << 16;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
   uint32_t ok;
   asm volatile(
     "{\n\t.reg .pred p;\n\t"
-    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
     "selp.u32 %0, 1, 0, p;\n\t}"
     : "=r"(ok)
-    : "r"(smem_u32(bar)), "r"(parity)
+    : "r"(smem_u32(bar)), "r"(parity), "r"(MBAR_SUSPEND_NS)
     : "memory");
   return ok != 0;
 }
-// Bounded wait on an mbarrier phase. Returns false when the limit ran out.
+// Bounded wait on an mbarrier phase. Returns false when the limit ran out.  Call it from ONE
+// thread and hand the result to the rest of the CTA through a barrier: hundreds of threads
+// polling the same mbarrier keep the shared-memory pipe busy for everybody else on the SM.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity)
 {
-  for (unsigned int i = 0; i < SPIN_LIMIT; ++i) {
+  for (unsigned int i = 0; i < MBAR_TRIES; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   return false;
@@ -177,6 +183,29 @@ __device__ __forceinline__ unsigned int lanemask_lt()
   unsigned int m;
   asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
   return m;
+}
+
+// Lanes of the warp that hold the same 8-bit digit as the caller (the caller included).
+// Built from one ballot per digit bit.  On B200 `match.any` costs time proportional to the number
+// of distinct values in the warp (about 60 SM-cycles for 30 distinct digits, measured), five
+// times more than eight ballots, so the ballot form is the default.
+#ifndef B2S_RANK_MATCH
+#define B2S_RANK_MATCH 0
+#endif
+__device__ __forceinline__ unsigned int warp_peers(unsigned int d)
+{
+#if B2S_RANK_MATCH
+  return __match_any_sync(0xFFFFFFFFu, d);
+#else
+  unsigned int peers = 0xFFFFFFFFu;
+#pragma unroll
+  for (int b = 0; b < RADIX_BITS; ++b) {
+    const bool bit         = (d >> b) & 1u;
+    const unsigned int bal = __ballot_sync(0xFFFFFFFFu, bit);
+    peers &= bit ? bal : ~bal;
+  }
+  return peers;
+#endif
 }
 
 __device__ __forceinline__ void raise_timeout(Ctrl* ctrl)

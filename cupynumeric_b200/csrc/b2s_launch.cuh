@@ -12,9 +12,33 @@ namespace b2s {
 constexpr unsigned int SEG_CAP = 8192;
 
 // Tile shape of the onesweep pass per key width / payload.
+// Compile-time overrides (-DB2S_CFG_...) exist for tuning sweeps.
+#ifndef B2S_CFG_THREADS_K
+#define B2S_CFG_THREADS_K 512
+#endif
+#ifndef B2S_CFG_THREADS_P
+#define B2S_CFG_THREADS_P 256
+#endif
+#ifndef B2S_CFG_ITEMS_K
+#define B2S_CFG_ITEMS_K 16
+#endif
+#ifndef B2S_CFG_ITEMS_P
+#define B2S_CFG_ITEMS_P 16
+#endif
+#ifndef B2S_CFG_CHAINS
+#define B2S_CFG_CHAINS 2
+#endif
+#ifndef B2S_CFG_MINCTAS_K
+#define B2S_CFG_MINCTAS_K 2
+#endif
+#ifndef B2S_CFG_MINCTAS_P
+#define B2S_CFG_MINCTAS_P 2
+#endif
 template <int KB, bool PAIRS> struct SweepCfg {
-  static constexpr int THREADS = (!PAIRS && KB <= 4) ? 512 : 256;
-  static constexpr int ITEMS   = 16;
+  static constexpr int THREADS = (!PAIRS && KB <= 4) ? B2S_CFG_THREADS_K : B2S_CFG_THREADS_P;
+  static constexpr int ITEMS   = (!PAIRS && KB <= 4) ? B2S_CFG_ITEMS_K : B2S_CFG_ITEMS_P;
+  static constexpr int CHAINS  = B2S_CFG_CHAINS;
+  static constexpr int MINCTAS = (!PAIRS && KB <= 4) ? B2S_CFG_MINCTAS_K : B2S_CFG_MINCTAS_P;
   static constexpr int TILE    = THREADS * ITEMS;
 };
 
@@ -49,8 +73,8 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
                                  int64_t index_offset, cudaStream_t stream)
 {
   using C   = SweepCfg<KB, PAIRS>;
-  using S   = SweepSmem<KB, PAIRS, C::THREADS, C::ITEMS>;
-  auto kern = onesweep_kernel<KB, XF, PAIRS, C::THREADS, C::ITEMS>;
+  using S   = SweepSmem<KB, PAIRS, C::THREADS, C::ITEMS, C::CHAINS>;
+  auto kern = onesweep_kernel<KB, XF, PAIRS, C::THREADS, C::ITEMS, C::CHAINS, C::MINCTAS>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::BYTES);
   if (e != cudaSuccess) return e;
   for (int pass = 0; pass < KB; ++pass) {

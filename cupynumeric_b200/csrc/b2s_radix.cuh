@@ -191,51 +191,61 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
 //
 // Key tiles (and index tiles) arrive by bulk asynchronous copy (TMA engine) when source and
 // size are 16-byte multiples; the last, partial tile and unaligned sources use plain loads.
+//
+// Ranking: a warp owns ITEMS*32 consecutive keys, element i of lane l at offset 32*i + l.  The
+// ITEMS elements are split into CHAINS groups of consecutive elements; each group has its own
+// row of 256 digit counters ("virtual warp"), so the CHAINS counter updates of one loop
+// iteration are independent of each other and their shared-memory latencies overlap.
 // ---------------------------------------------------------------------------------------------
 constexpr unsigned int LB_FLAG_AGG  = 1u << 30;  // tile count published
 constexpr unsigned int LB_FLAG_INCL = 2u << 30;  // inclusive prefix published
 constexpr unsigned int LB_VALUE     = (1u << 30) - 1;
 constexpr unsigned int MAX_N_1D     = 1u << 30;  // counts must fit 30 bits
+#ifndef B2S_CFG_LB_WINDOW
+#define B2S_CFG_LB_WINDOW 8
+#endif
+constexpr int LB_WINDOW             = B2S_CFG_LB_WINDOW;  // predecessors inspected per round trip
 
-template <int KB, bool PAIRS, int THREADS, int ITEMS>
+template <int KB, bool PAIRS, int THREADS, int ITEMS, int CHAINS>
 struct SweepSmem {
   static constexpr int TILE  = THREADS * ITEMS;
   static constexpr int WARPS = THREADS / 32;
-  // staging buffer: key tile, reused for the sorted keys, then (pairs) for the sorted indices
-  static constexpr size_t STAGE_BYTES = (size_t)TILE * (PAIRS ? 8 : KB);
-  static constexpr size_t VAL_BYTES   = PAIRS ? (size_t)TILE * 8 : 0;  // index tile as loaded
-  static constexpr size_t OFF_VALS    = STAGE_BYTES;
-  static constexpr size_t OFF_WHIST   = OFF_VALS + VAL_BYTES;
-  static constexpr size_t OFF_EXCL    = OFF_WHIST + (size_t)WARPS * RADIX * 4;
-  static constexpr size_t OFF_BASE    = OFF_EXCL + RADIX * 4;
-  static constexpr size_t OFF_BAR     = OFF_BASE + RADIX * 4;
-  static constexpr size_t OFF_MISC    = OFF_BAR + 8;
-  static constexpr size_t BYTES       = OFF_MISC + 8;
+  static constexpr int ROWS  = WARPS * CHAINS;  // counter rows ("virtual warps")
+  static constexpr size_t KEY_BYTES = ((size_t)TILE * KB + 127) / 128 * 128;
+  static constexpr size_t VAL_BYTES = PAIRS ? (size_t)TILE * 8 : 0;
+  static constexpr size_t OFF_VALS  = KEY_BYTES;
+  static constexpr size_t OFF_HIST  = OFF_VALS + VAL_BYTES;
+  static constexpr size_t OFF_EXCL  = OFF_HIST + (size_t)ROWS * RADIX * 4;
+  static constexpr size_t OFF_BASE  = OFF_EXCL + RADIX * 4;
+  static constexpr size_t OFF_BAR   = OFF_BASE + RADIX * 4;
+  static constexpr size_t OFF_MISC  = OFF_BAR + 8;
+  static constexpr size_t BYTES     = OFF_MISC + 8;
 };
 
-template <int KB, int XF, bool PAIRS, int THREADS, int ITEMS>
-__global__ void __launch_bounds__(THREADS)
+template <int KB, int XF, bool PAIRS, int THREADS, int ITEMS, int CHAINS, int MIN_CTAS>
+__global__ void __launch_bounds__(THREADS, MIN_CTAS)
 onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsigned int n, int64_t index_offset)
 {
   using K = typename KeyOf<KB>::type;
-  using S = SweepSmem<KB, PAIRS, THREADS, ITEMS>;
+  using S = SweepSmem<KB, PAIRS, THREADS, ITEMS, CHAINS>;
   constexpr int TILE  = S::TILE;
-  constexpr int WARPS = S::WARPS;
+  constexpr int ROWS  = S::ROWS;
+  constexpr int IPC   = ITEMS / CHAINS;  // items per chain
   static_assert(THREADS >= RADIX, "one thread per digit is needed for the look-back");
+  static_assert(ITEMS % CHAINS == 0, "chains split the items evenly");
 
   const PassDesc pd = ctrl->pass[pass];
   if (!pd.active) return;
   if (ld_relaxed(&ctrl->abort)) return;
 
   extern __shared__ __align__(128) unsigned char smem[];
-  K* stage_keys           = reinterpret_cast<K*>(smem);
-  int64_t* stage_vals     = reinterpret_cast<int64_t*>(smem);
-  int64_t* in_vals        = reinterpret_cast<int64_t*>(smem + S::OFF_VALS);
-  unsigned int* warp_hist = reinterpret_cast<unsigned int*>(smem + S::OFF_WHIST);
-  unsigned int* dig_excl  = reinterpret_cast<unsigned int*>(smem + S::OFF_EXCL);
-  unsigned int* base_ml   = reinterpret_cast<unsigned int*>(smem + S::OFF_BASE);
-  uint64_t* bar           = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
-  unsigned int* misc      = reinterpret_cast<unsigned int*>(smem + S::OFF_MISC);
+  K* stage_keys          = reinterpret_cast<K*>(smem);
+  int64_t* stage_vals    = reinterpret_cast<int64_t*>(smem + S::OFF_VALS);
+  unsigned int* hist     = reinterpret_cast<unsigned int*>(smem + S::OFF_HIST);
+  unsigned int* dig_excl = reinterpret_cast<unsigned int*>(smem + S::OFF_EXCL);
+  unsigned int* base_ml  = reinterpret_cast<unsigned int*>(smem + S::OFF_BASE);
+  uint64_t* bar          = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  unsigned int* misc     = reinterpret_cast<unsigned int*>(smem + S::OFF_MISC);
 
   const int tid  = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -249,7 +259,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
     mbar_init(bar, 1);
     fence_mbar_init();
   }
-  for (int i = tid; i < WARPS * RADIX; i += THREADS) warp_hist[i] = 0;
+  for (int i = tid; i < ROWS * RADIX; i += THREADS) hist[i] = 0;
   __syncthreads();
   const unsigned int tile      = misc[0];
   const unsigned int tile_base = tile * TILE;
@@ -264,13 +274,15 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   K key[ITEMS];
   const int stripe0 = warp * (ITEMS * 32) + lane;  // element i of this thread sits at stripe0 + 32*i
   if (use_bulk) {
+    int arrived = 1;
     if (tid == 0) {
       const uint32_t bytes = (uint32_t)(TILE * KB) + (load_idx ? (uint32_t)(TILE * 8) : 0u);
       mbar_expect_tx(bar, bytes);
       bulk_load(stage_keys, src_keys + tile_base, TILE * KB, bar);
-      if (load_idx) bulk_load(in_vals, src_idx + tile_base, TILE * 8, bar);
+      if (load_idx) bulk_load(stage_vals, src_idx + tile_base, TILE * 8, bar);
+      arrived = mbar_wait_bounded(bar, 0);  // one thread waits; the others park at the barrier
     }
-    if (!mbar_wait_bounded(bar, 0)) {
+    if (!__syncthreads_and(arrived)) {
       // The copy never signalled: record it and leave. Nothing was published for this tile, so
       // later tiles see `abort` in their own look-back loop and leave as well.
       if (tid == 0) raise_timeout(ctrl);
@@ -289,50 +301,56 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
         const unsigned int e = stripe0 + 32 * i;
-        in_vals[e]           = e < valid ? src_idx[tile_base + e] : 0;
+        stage_vals[e]        = e < valid ? src_idx[tile_base + e] : 0;
       }
     }
   }
 
   // ---- stable in-warp ranking by digit: match lanes holding the same digit ----
-  unsigned int rank[ITEMS];
-  unsigned int* my_hist = warp_hist + warp * RADIX;
+  // rd[i] packs the element's digit (bits 16..23) with its rank among the same digit inside its
+  // chain (bits 0..15).
+  unsigned int rd[ITEMS];
+  unsigned int* my_hist = hist + (warp * CHAINS) * RADIX;
   const unsigned int lt = lanemask_lt();
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const unsigned int d     = digit_of<KB, XF>(key[i], shift);
-    const unsigned int peers = __match_any_sync(0xFFFFFFFFu, d);
-    const unsigned int below = peers & lt;
-    unsigned int old         = 0;
-    if (below == 0) {  // lowest lane of the group owns the counter update
-      old        = my_hist[d];
-      my_hist[d] = old + __popc(peers);
+  for (int k = 0; k < IPC; ++k) {
+    unsigned int d[CHAINS], peers[CHAINS], old[CHAINS];
+#pragma unroll
+    for (int c = 0; c < CHAINS; ++c) {
+      d[c]     = digit_of<KB, XF>(key[c * IPC + k], shift);
+      peers[c] = warp_peers(d[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < CHAINS; ++c) old[c] = my_hist[c * RADIX + d[c]];
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < CHAINS; ++c) {
+      if ((peers[c] & lt) == 0) my_hist[c * RADIX + d[c]] = old[c] + __popc(peers[c]);
     }
     __syncwarp();
-    old     = __shfl_sync(0xFFFFFFFFu, old, __ffs(peers) - 1);
-    rank[i] = old + __popc(below);
+#pragma unroll
+    for (int c = 0; c < CHAINS; ++c) rd[c * IPC + k] = (d[c] << 16) | (old[c] + __popc(peers[c] & lt));
   }
   __syncthreads();
 
-  // ---- per-digit tile counts: exclusive scan over warps, then over digits ----
+  // ---- per-digit tile counts: exclusive scan over counter rows, then over digits ----
   unsigned int my_count = 0;
   if (tid < RADIX) {
     unsigned int run = 0;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) {
-      const unsigned int t       = warp_hist[w * RADIX + tid];
-      warp_hist[w * RADIX + tid] = run;
+    for (int r = 0; r < ROWS; ++r) {
+      const unsigned int t  = hist[r * RADIX + tid];
+      hist[r * RADIX + tid] = run;
       run += t;
     }
     my_count = run;
-    // exclusive scan of the 256 counts
     unsigned int incl = run;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
       if (lane >= o) incl += t;
     }
-    if (lane == 31) base_ml[warp] = incl;  // scratch: warp totals (8 of them)
+    if (lane == 31) base_ml[warp] = incl;  // scratch: totals of the 8 digit groups
     dig_excl[tid] = incl - run;
   }
   __syncthreads();
@@ -346,29 +364,49 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
 
   // ---- chained prefix over tiles (decoupled look-back), one thread per digit ----
   if (tid < RADIX) {
-    dig_excl[tid]       = my_excl_tile;
-    unsigned int* mine  = lookback + (size_t)tile * RADIX + tid;
-    unsigned int excl   = 0;
+    dig_excl[tid]      = my_excl_tile;
+    unsigned int* mine = lookback + (size_t)tile * RADIX + tid;
+    unsigned int excl  = 0;
     if (tile == 0) {
       st_relaxed(mine, LB_FLAG_INCL | my_count);
     } else {
       st_relaxed(mine, LB_FLAG_AGG | my_count);
-      unsigned int t     = tile - 1;
+      // Walk back over the predecessors, LB_WINDOW of them per round trip: the loads of one
+      // window are independent, so a run of tiles that have only published their counts costs
+      // one memory latency per window instead of one per tile.
+      int t              = (int)tile - 1;
       unsigned int spins = 0;
       bool gave_up       = false;
-      while (true) {
-        const unsigned int v = ld_relaxed(lookback + (size_t)t * RADIX + tid);
-        const unsigned int f = v >> 30;
-        if (f == 0) {
+      bool done          = false;
+#ifdef B2S_EXP_NO_LOOKBACK
+      done = true;
+#endif
+      while (!done) {
+        unsigned int v[LB_WINDOW];
+#pragma unroll
+        for (int j = 0; j < LB_WINDOW; ++j) {
+          const int tj = t - j;
+          v[j]         = tj >= 0 ? ld_relaxed(lookback + (size_t)tj * RADIX + tid) : LB_FLAG_INCL;
+        }
+        int used = 0;
+#pragma unroll
+        for (int j = 0; j < LB_WINDOW; ++j) {
+          if (!done && used == j) {
+            const unsigned int f = v[j] >> 30;
+            if (f != 0) {
+              excl += v[j] & LB_VALUE;
+              ++used;
+              if (f == 2) done = true;
+            }
+          }
+        }
+        t -= used;
+        if (!done && used == 0) {
           if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && ld_relaxed(&ctrl->abort))) {
             gave_up = true;
             break;
           }
-          continue;
         }
-        excl += v & LB_VALUE;
-        if (f == 2 || t == 0) break;
-        --t;
       }
       if (gave_up) raise_timeout(ctrl);
       st_relaxed(mine, LB_FLAG_INCL | ((excl + my_count) & LB_VALUE));
@@ -378,45 +416,40 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   }
   __syncthreads();
 
-  // ---- scatter keys through shared memory ----
+  // ---- permute the tile inside shared memory: position = digit start + earlier rows + rank ----
   unsigned int pos[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    const unsigned int d = digit_of<KB, XF>(key[i], shift);
-    pos[i]               = dig_excl[d] + my_hist[d] + rank[i];
+    const unsigned int d = rd[i] >> 16;
+    pos[i]               = dig_excl[d] + my_hist[(i / IPC) * RADIX + d] + (rd[i] & 0xFFFFu);
     stage_keys[pos[i]]   = key[i];
   }
+  if (PAIRS) {
+    int64_t val[ITEMS];
+    if (load_idx) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) val[i] = stage_vals[stripe0 + 32 * i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) val[i] = index_offset + (int64_t)(tile_base + stripe0 + 32 * i);
+    }
+    __syncthreads();  // every thread holds its indices before any slot is overwritten
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) stage_vals[pos[i]] = val[i];
+  }
   __syncthreads();
-  K* dst_keys = static_cast<K*>(pd.dst_keys);
-  unsigned int gidx[PAIRS ? ITEMS : 1];
+
+  // ---- coalesced scatter: consecutive threads store consecutive elements of a digit's run ----
+  K* dst_keys      = static_cast<K*>(pd.dst_keys);
+  int64_t* dst_idx = pd.dst_idx;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const unsigned int p = i * THREADS + tid;
     const K k            = stage_keys[p];
     const unsigned int g = base_ml[digit_of<KB, XF>(k, shift)] + p;
-    if (PAIRS) gidx[i] = g;
-    if (dst_keys != nullptr && p < valid) dst_keys[g] = k;
-  }
-
-  // ---- indices follow the same permutation ----
-  if (PAIRS) {
-    int64_t val[ITEMS];
-    if (load_idx) {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) val[i] = in_vals[stripe0 + 32 * i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) val[i] = index_offset + (int64_t)(tile_base + stripe0 + 32 * i);
-    }
-    __syncthreads();  // every thread is done reading the staged keys
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) stage_vals[pos[i]] = val[i];
-    __syncthreads();
-    int64_t* dst_idx = pd.dst_idx;
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) {
-      const unsigned int p = i * THREADS + tid;
-      if (p < valid) dst_idx[gidx[i]] = stage_vals[p];
+    if (p < valid) {
+      if (dst_keys != nullptr) dst_keys[g] = k;
+      if (PAIRS) dst_idx[g] = stage_vals[p];
     }
   }
 }

@@ -67,19 +67,19 @@ segsort_kernel(const typename KeyOf<KB>::type* __restrict__ in, typename KeyOf<K
     const K* src = in + seg * seg_len;
     const bool use_bulk = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && (seg_bytes % 16 == 0);
     if (use_bulk) {
+      for (unsigned int e = seg_len + tid; e < TILE; e += THREADS) skeys[e] = pad;
+      int arrived = 1;
       if (tid == 0) {
         fence_proxy_async();  // earlier generic accesses to the buffer are ordered before the copy
         mbar_expect_tx(bar, (uint32_t)seg_bytes);
         bulk_load(skeys, src, (uint32_t)seg_bytes, bar);
+        arrived = mbar_wait_bounded(bar, phase);  // one thread waits; the others park at the barrier
       }
-      for (unsigned int e = seg_len + tid; e < TILE; e += THREADS) skeys[e] = pad;
-      const bool ok = mbar_wait_bounded(bar, phase);
       phase ^= 1u;
-      if (!ok) {
+      if (!__syncthreads_and(arrived)) {
         if (tid == 0) raise_timeout(ctrl);
         return;
       }
-      __syncthreads();  // padding written by other threads
     } else {
       for (unsigned int e = tid; e < TILE; e += THREADS) skeys[e] = e < seg_len ? src[e] : pad;
       __syncthreads();
@@ -132,7 +132,7 @@ segsort_kernel(const typename KeyOf<KB>::type* __restrict__ in, typename KeyOf<K
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) {
         const unsigned int d     = (unsigned int)(to_ordered_rt<KB>(key[i], xf) >> shift) & 0xFFu;
-        const unsigned int peers = __match_any_sync(0xFFFFFFFFu, d);
+        const unsigned int peers = warp_peers(d);
         const unsigned int below = peers & lt;
         unsigned int old         = 0;
         if (below == 0) {
