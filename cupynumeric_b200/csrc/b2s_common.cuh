@@ -192,20 +192,65 @@ __device__ __forceinline__ unsigned int lanemask_lt()
 #ifndef B2S_RANK_MATCH
 #define B2S_RANK_MATCH 0
 #endif
+template <int B>
+__device__ __forceinline__ void ballot_step(unsigned int d, unsigned int& differs)
+{
+  // the caller's bit B replicated over a word: 0 or 0xFFFFFFFF
+  const int mine         = (int)(d << (31 - B)) >> 31;
+  const unsigned int bal = __ballot_sync(0xFFFFFFFFu, mine < 0);
+  differs |= bal ^ (unsigned int)mine;
+}
+
 __device__ __forceinline__ unsigned int warp_peers(unsigned int d)
 {
 #if B2S_RANK_MATCH
   return __match_any_sync(0xFFFFFFFFu, d);
 #else
-  unsigned int peers = 0xFFFFFFFFu;
-#pragma unroll
-  for (int b = 0; b < RADIX_BITS; ++b) {
-    const bool bit         = (d >> b) & 1u;
-    const unsigned int bal = __ballot_sync(0xFFFFFFFFu, bit);
-    peers &= bit ? bal : ~bal;
-  }
-  return peers;
+  // A lane differs from the caller in bit b exactly where (ballot_b ^ mine_b) is set, mine_b being
+  // the caller's own bit replicated over the word; the peers are the lanes that differ nowhere.
+  // The per-bit step is PTX so that it stays a test, a vote and a select.
+  unsigned int differs = 0;
+  ballot_step<0>(d, differs);
+  ballot_step<1>(d, differs);
+  ballot_step<2>(d, differs);
+  ballot_step<3>(d, differs);
+  ballot_step<4>(d, differs);
+  ballot_step<5>(d, differs);
+  ballot_step<6>(d, differs);
+  ballot_step<7>(d, differs);
+  return ~differs;
 #endif
+}
+
+// Digit extraction with the per-pass constants hoisted out of the per-key work.
+struct DigitSel {
+  unsigned int prmt;   // byte-permute selector that moves the pass's byte to bits 0..7
+  unsigned int flip;   // xor applied to the extracted byte (sign bit of signed keys, top pass only)
+  int hi_word;         // 64-bit keys: the digit lives in the upper word
+};
+template <int KB, int XF>
+__device__ __forceinline__ DigitSel make_digit_sel(int pass)
+{
+  DigitSel s;
+  s.prmt    = 0x4440u | (unsigned int)(pass & 3);
+  s.flip    = (XF == XF_SIGNED && pass == KB - 1) ? 0x80u : 0u;
+  s.hi_word = pass >= 4;
+  return s;
+}
+template <int KB, int XF>
+__device__ __forceinline__ unsigned int digit_fast(typename KeyOf<KB>::type raw, const DigitSel& s, int shift)
+{
+  if (XF == XF_FLOAT) {
+    return (unsigned int)(to_ordered<KB, XF>(raw) >> shift) & (RADIX - 1);
+  } else if (KB == 8) {
+    const unsigned long long r64 = (unsigned long long)raw;
+    const unsigned int w         = s.hi_word ? (unsigned int)(r64 >> 32) : (unsigned int)r64;
+    return __byte_perm(w, 0u, s.prmt) ^ s.flip;
+  } else if (KB == 4) {
+    return __byte_perm((unsigned int)raw, 0u, s.prmt) ^ s.flip;
+  } else {
+    return (((unsigned int)raw >> shift) & (RADIX - 1)) ^ s.flip;
+  }
 }
 
 __device__ __forceinline__ void raise_timeout(Ctrl* ctrl)

@@ -12,33 +12,57 @@ namespace b2s {
 constexpr unsigned int SEG_CAP = 8192;
 
 // Tile shape of the onesweep pass per key width / payload.
-// Compile-time overrides (-DB2S_CFG_...) exist for tuning sweeps.
-#ifndef B2S_CFG_THREADS_K
-#define B2S_CFG_THREADS_K 512
-#endif
-#ifndef B2S_CFG_THREADS_P
-#define B2S_CFG_THREADS_P 256
-#endif
-#ifndef B2S_CFG_ITEMS_K
-#define B2S_CFG_ITEMS_K 16
-#endif
-#ifndef B2S_CFG_ITEMS_P
-#define B2S_CFG_ITEMS_P 16
-#endif
+// Tile shapes found by sweeps on B200 (2^28 keys): more keys per thread amortise the per-tile
+// work (counter zeroing, row scan, look-back); pairs run three CTAs per SM.
+// -DB2S_CFG_<group>_{THREADS,ITEMS,MINCTAS} override a group for tuning sweeps; groups are
+// K4 (keys only, <= 4-byte keys), K8 (keys only, 8-byte keys), P4 / P8 (key + index).
 #ifndef B2S_CFG_CHAINS
-#define B2S_CFG_CHAINS 2
+#define B2S_CFG_CHAINS 1
 #endif
-#ifndef B2S_CFG_MINCTAS_K
-#define B2S_CFG_MINCTAS_K 2
+#ifndef B2S_CFG_K4_THREADS
+#define B2S_CFG_K4_THREADS 512
 #endif
-#ifndef B2S_CFG_MINCTAS_P
-#define B2S_CFG_MINCTAS_P 2
+#ifndef B2S_CFG_K4_ITEMS
+#define B2S_CFG_K4_ITEMS 20
+#endif
+#ifndef B2S_CFG_K4_MINCTAS
+#define B2S_CFG_K4_MINCTAS 2
+#endif
+#ifndef B2S_CFG_K8_THREADS
+#define B2S_CFG_K8_THREADS 256
+#endif
+#ifndef B2S_CFG_K8_ITEMS
+#define B2S_CFG_K8_ITEMS 24
+#endif
+#ifndef B2S_CFG_K8_MINCTAS
+#define B2S_CFG_K8_MINCTAS 3
+#endif
+#ifndef B2S_CFG_P4_THREADS
+#define B2S_CFG_P4_THREADS 256
+#endif
+#ifndef B2S_CFG_P4_ITEMS
+#define B2S_CFG_P4_ITEMS 20
+#endif
+#ifndef B2S_CFG_P4_MINCTAS
+#define B2S_CFG_P4_MINCTAS 3
+#endif
+#ifndef B2S_CFG_P8_THREADS
+#define B2S_CFG_P8_THREADS 256
+#endif
+#ifndef B2S_CFG_P8_ITEMS
+#define B2S_CFG_P8_ITEMS 24
+#endif
+#ifndef B2S_CFG_P8_MINCTAS
+#define B2S_CFG_P8_MINCTAS 2
 #endif
 template <int KB, bool PAIRS> struct SweepCfg {
-  static constexpr int THREADS = (!PAIRS && KB <= 4) ? B2S_CFG_THREADS_K : B2S_CFG_THREADS_P;
-  static constexpr int ITEMS   = (!PAIRS && KB <= 4) ? B2S_CFG_ITEMS_K : B2S_CFG_ITEMS_P;
+  static constexpr int THREADS = PAIRS ? (KB == 8 ? B2S_CFG_P8_THREADS : B2S_CFG_P4_THREADS)
+                                       : (KB == 8 ? B2S_CFG_K8_THREADS : B2S_CFG_K4_THREADS);
+  static constexpr int ITEMS   = PAIRS ? (KB == 8 ? B2S_CFG_P8_ITEMS : B2S_CFG_P4_ITEMS)
+                                       : (KB == 8 ? B2S_CFG_K8_ITEMS : B2S_CFG_K4_ITEMS);
+  static constexpr int MINCTAS = PAIRS ? (KB == 8 ? B2S_CFG_P8_MINCTAS : B2S_CFG_P4_MINCTAS)
+                                       : (KB == 8 ? B2S_CFG_K8_MINCTAS : B2S_CFG_K4_MINCTAS);
   static constexpr int CHAINS  = B2S_CFG_CHAINS;
-  static constexpr int MINCTAS = (!PAIRS && KB <= 4) ? B2S_CFG_MINCTAS_K : B2S_CFG_MINCTAS_P;
   static constexpr int TILE    = THREADS * ITEMS;
 };
 

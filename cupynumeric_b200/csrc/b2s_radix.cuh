@@ -202,7 +202,7 @@ constexpr unsigned int LB_FLAG_INCL = 2u << 30;  // inclusive prefix published
 constexpr unsigned int LB_VALUE     = (1u << 30) - 1;
 constexpr unsigned int MAX_N_1D     = 1u << 30;  // counts must fit 30 bits
 #ifndef B2S_CFG_LB_WINDOW
-#define B2S_CFG_LB_WINDOW 8
+#define B2S_CFG_LB_WINDOW 1
 #endif
 constexpr int LB_WINDOW             = B2S_CFG_LB_WINDOW;  // predecessors inspected per round trip
 
@@ -249,7 +249,8 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
 
   const int tid  = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
-  const int shift = pass * RADIX_BITS;
+  const int shift   = pass * RADIX_BITS;
+  const DigitSel ds = make_digit_sel<KB, XF>(pass);
 
   const K* src_keys      = static_cast<const K*>(pd.src_keys);
   const int64_t* src_idx = pd.src_idx;
@@ -317,16 +318,15 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
     unsigned int d[CHAINS], peers[CHAINS], old[CHAINS];
 #pragma unroll
     for (int c = 0; c < CHAINS; ++c) {
-      d[c]     = digit_of<KB, XF>(key[c * IPC + k], shift);
+      d[c]     = digit_fast<KB, XF>(key[c * IPC + k], ds, shift);
       peers[c] = warp_peers(d[c]);
     }
 #pragma unroll
     for (int c = 0; c < CHAINS; ++c) old[c] = my_hist[c * RADIX + d[c]];
     __syncwarp();
 #pragma unroll
-    for (int c = 0; c < CHAINS; ++c) {
-      if ((peers[c] & lt) == 0) my_hist[c * RADIX + d[c]] = old[c] + __popc(peers[c]);
-    }
+    // every lane of a group stores the same value to the same counter: no leader election needed
+    for (int c = 0; c < CHAINS; ++c) my_hist[c * RADIX + d[c]] = old[c] + __popc(peers[c]);
     __syncwarp();
 #pragma unroll
     for (int c = 0; c < CHAINS; ++c) rd[c * IPC + k] = (d[c] << 16) | (old[c] + __popc(peers[c] & lt));
@@ -440,16 +440,28 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   __syncthreads();
 
   // ---- coalesced scatter: consecutive threads store consecutive elements of a digit's run ----
-  K* dst_keys      = static_cast<K*>(pd.dst_keys);
-  int64_t* dst_idx = pd.dst_idx;
+  K* dst_keys       = static_cast<K*>(__builtin_assume_aligned(pd.dst_keys, sizeof(K)));
+  int64_t* dst_idx  = pd.dst_idx;
+  const bool wr_key = dst_keys != nullptr;
+  if (full) {
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const unsigned int p = i * THREADS + tid;
-    const K k            = stage_keys[p];
-    const unsigned int g = base_ml[digit_of<KB, XF>(k, shift)] + p;
-    if (p < valid) {
-      if (dst_keys != nullptr) dst_keys[g] = k;
-      if (PAIRS) dst_idx[g] = stage_vals[p];
+    for (int i = 0; i < ITEMS; ++i) {
+      const unsigned int p = i * THREADS + tid;
+      const K k            = stage_keys[p];
+      const unsigned int g = base_ml[digit_fast<KB, XF>(k, ds, shift)] + p;
+      if (wr_key) __stcg(dst_keys + g, k);
+      if (PAIRS) __stcg(reinterpret_cast<long long*>(dst_idx) + g, (long long)stage_vals[p]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+      const unsigned int p = i * THREADS + tid;
+      const K k            = stage_keys[p];
+      const unsigned int g = base_ml[digit_fast<KB, XF>(k, ds, shift)] + p;
+      if (p < valid) {
+        if (wr_key) dst_keys[g] = k;
+        if (PAIRS) dst_idx[g] = stage_vals[p];
+      }
     }
   }
 }

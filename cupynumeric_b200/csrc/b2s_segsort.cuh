@@ -133,15 +133,11 @@ segsort_kernel(const typename KeyOf<KB>::type* __restrict__ in, typename KeyOf<K
       for (int i = 0; i < ITEMS; ++i) {
         const unsigned int d     = (unsigned int)(to_ordered_rt<KB>(key[i], xf) >> shift) & 0xFFu;
         const unsigned int peers = warp_peers(d);
-        const unsigned int below = peers & lt;
-        unsigned int old         = 0;
-        if (below == 0) {
-          old        = my_hist[d];
-          my_hist[d] = old + __popc(peers);
-        }
+        const unsigned int old   = my_hist[d];
         __syncwarp();
-        old     = __shfl_sync(0xFFFFFFFFu, old, __ffs(peers) - 1);
-        rank[i] = old + __popc(below);
+        my_hist[d] = old + __popc(peers);  // same value from every lane of the group
+        __syncwarp();
+        rank[i] = old + __popc(peers & lt);
       }
       __syncthreads();
       // exclusive scan over warps for each digit
