@@ -71,6 +71,14 @@ def nccl_paths():
     return None, None
 
 
+# callback types of b2s_dist_sort_1d
+ALLOC_FN = ctypes.CFUNCTYPE(ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t)
+FREE_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p)
+BARRIER_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p)
+
+# layout of one sample record (see include/b200sort.h)
+SAMPLE_DTYPE = np.dtype([("okey", np.uint64), ("pos", np.int64), ("rank", np.int32), ("valid", np.int32)])
+
 _lib = None
 
 _P, _SZ, _I, _I64 = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int64
@@ -82,6 +90,18 @@ SIGNATURES = {
     "b2s_workspace_bytes": (_I, [_I, _SZ, _SZ, _I, ctypes.POINTER(_SZ)]),
     "b2s_local_sort": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _I, _I, _P, _SZ, _P]),
     "b2s_check_status": (_I, [_P, _P]),
+    "b2s_dist_sort_1d": (_I, [_I, _P, _SZ, _I64, _I, _P, _I, _I, _P, _P, _P, _P, _P,
+                               ctypes.POINTER(_P), ctypes.POINTER(_SZ), _P]),
+    "b2s_kway_merge_workspace_bytes": (_I, [_SZ, _I, ctypes.POINTER(_SZ)]),
+    "b2s_kway_merge": (_I, [_I, _I, _P, _P, _P, _P, _P, _SZ, _P]),
+    "b2s_nccl_unique_id": (_I, [_P]),
+    "b2s_nccl_comm_create": (_I, [ctypes.POINTER(_P), _I, _P, _I]),
+    "b2s_nccl_comm_destroy": (_I, [_P]),
+    "b2s_samples_per_rank": (_I, []),
+    "b2s_host_sample_position": (ctypes.c_longlong, [ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
+    "b2s_host_sort_samples": (None, [_P, _SZ]),
+    "b2s_host_select_splitters": (_I, [_P, _SZ, _I, _P]),
+    "b2s_host_cut_position": (ctypes.c_longlong, [_P, _I, ctypes.c_longlong, ctypes.c_longlong]),
     "b2s_profile_enable": (_I, [_I]),
     "b2s_profile_read": (_I, [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_ulonglong)]),
     "b2s_launch_count": (ctypes.c_ulonglong, [_I]),

@@ -1,0 +1,409 @@
+// Distributed 1-D sort over the GPUs of one NVSwitch box: local sort -> regular oversampling ->
+// NCCL all-gather of samples -> splitters -> cut positions -> NCCL all-gather of counts ->
+// one grouped send/recv exchange of keys (and indices) -> stable k-way merge.
+// Replaces sample_sort_nccl_nd for 1-D arrays (src/cupynumeric/sort/sort.cu:1270-1784) and the
+// surrounding buffer handling of SortImplBody<GPU> (sort.cu:1797-1940).
+#include <nccl.h>
+
+#include <algorithm>
+#include <cstring>
+#include <type_traits>
+#include <vector>
+
+#include "../../include/b200sort.h"
+#include "b2s_common.cuh"
+#include "b2s_dist_host.h"
+#include "b2s_merge.cuh"
+#include "b2s_prof.h"
+
+namespace b2s {
+
+static int kb_of(int dtype, int* xf)
+{
+  switch (dtype) {
+    case B2S_BOOL: *xf = XF_UNSIGNED; return 1;
+    case B2S_INT8: *xf = XF_SIGNED; return 1;
+    case B2S_UINT8: *xf = XF_UNSIGNED; return 1;
+    case B2S_INT16: *xf = XF_SIGNED; return 2;
+    case B2S_UINT16: *xf = XF_UNSIGNED; return 2;
+    case B2S_FLOAT16: *xf = XF_FLOAT; return 2;
+    case B2S_INT32: *xf = XF_SIGNED; return 4;
+    case B2S_UINT32: *xf = XF_UNSIGNED; return 4;
+    case B2S_FLOAT32: *xf = XF_FLOAT; return 4;
+    case B2S_INT64: *xf = XF_SIGNED; return 8;
+    case B2S_UINT64: *xf = XF_UNSIGNED; return 8;
+    case B2S_FLOAT64: *xf = XF_FLOAT; return 8;
+    default: return 0;
+  }
+}
+
+// Regular samples of the locally sorted keys, as (ordered key, rank, position) triples.
+template <int KB>
+__global__ void sample_kernel(const void* sorted, long long n, int s, int rank, int xf, Sample* out)
+{
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= s) return;
+  Sample sm;
+  const long long s_eff = n < s ? n : s;
+  if (j < s_eff) {
+    const long long p = sample_position(j, s_eff, n);
+    sm.okey  = okey_at<KB>(sorted, p, xf);
+    sm.pos   = p;
+    sm.rank  = rank;
+    sm.valid = 1;
+  } else {
+    sm.okey = ~0ull;
+    sm.pos = 0;
+    sm.rank = rank;
+    sm.valid = 0;
+  }
+  out[j] = sm;
+}
+
+// cuts[k] for k = 1..nranks-1: how many of my sorted elements go to ranks < k.
+template <int KB>
+__global__ void cut_kernel(const void* sorted, long long n, const Sample* splitters, int nranks, int rank,
+                           int xf, long long* cuts)
+{
+  const int k = blockIdx.x * blockDim.x + threadIdx.x + 1;
+  if (k >= nranks) return;
+  const Sample sp = splitters[k - 1];
+  long long c;
+  if (!sp.valid) {
+    c = n;  // no populated sample anywhere right of this splitter
+  } else {
+    const long long lower = lower_bound_okey<KB>(sorted, 0, n, sp.okey, xf);
+    const long long upper = sp.okey == ~0ull ? n : lower_bound_okey<KB>(sorted, lower, n, sp.okey + 1, xf);
+    c = cut_position(sp, rank, lower, upper);
+  }
+  cuts[k] = c;
+  if (k == 1) {
+    cuts[0]      = 0;
+    cuts[nranks] = n;
+  }
+}
+
+template <typename F>
+static cudaError_t by_width(int kb, F&& f)
+{
+  switch (kb) {
+    case 1: return f(std::integral_constant<int, 1>{});
+    case 2: return f(std::integral_constant<int, 2>{});
+    case 4: return f(std::integral_constant<int, 4>{});
+    default: return f(std::integral_constant<int, 8>{});
+  }
+}
+
+struct Scratch {
+  b2s_alloc_fn alloc;
+  b2s_free_fn release;
+  void* ctx;
+  std::vector<void*> owned;
+  void* get(size_t bytes)
+  {
+    void* p = alloc(ctx, bytes ? bytes : 256);
+    if (p) owned.push_back(p);
+    return p;
+  }
+  void drop(void* p)
+  {
+    for (auto& q : owned)
+      if (q == p) { q = nullptr; }
+    if (p && release) release(ctx, p);
+  }
+  // keep `p` alive past the call (ownership passes to the caller)
+  void disown(void* p)
+  {
+    for (auto& q : owned)
+      if (q == p) q = nullptr;
+  }
+  ~Scratch()
+  {
+    for (void* q : owned)
+      if (q && release) release(ctx, q);
+  }
+};
+
+// Launches the partition and merge kernels for `runs` (total elements) into `out`.
+static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bool args, void* out,
+                      long long* d_tcuts, cudaStream_t stream)
+{
+  const long long ntiles = (total + MERGE_TILE - 1) / MERGE_TILE;
+  cudaError_t e = by_width(kb, [&](auto w) {
+    constexpr int KB = decltype(w)::value;
+    {
+      prof::Scope ps(prof::K_DIST, stream);
+      const long long warps = ntiles + 1;
+      merge_partition_kernel<KB><<<(unsigned int)((warps + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts);
+    }
+    prof::Scope ps(prof::K_MERGE, stream);
+    if (args) {
+      auto kern = merge_tiles_kernel<KB, true>;
+      cudaError_t ee = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MergeSmem<KB, true>::BYTES);
+      if (ee != cudaSuccess) return ee;
+      kern<<<(unsigned int)ntiles, MERGE_THREADS, MergeSmem<KB, true>::BYTES, stream>>>(runs, total, xf, d_tcuts, out);
+    } else {
+      auto kern = merge_tiles_kernel<KB, false>;
+      cudaError_t ee = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MergeSmem<KB, false>::BYTES);
+      if (ee != cudaSuccess) return ee;
+      kern<<<(unsigned int)ntiles, MERGE_THREADS, MergeSmem<KB, false>::BYTES, stream>>>(runs, total, xf, d_tcuts, out);
+    }
+    return cudaGetLastError();
+  });
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
+}
+
+#define CK_CUDA(x) do { if ((x) != cudaSuccess) return B2S_ERR_CUDA; } while (0)
+#define CK_NCCL(x) do { if ((x) != ncclSuccess) return B2S_ERR_NCCL; } while (0)
+
+}  // namespace b2s
+
+using namespace b2s;
+
+extern "C" {
+
+void b2s_host_sort_samples(void* samples, size_t count)
+{
+  Sample* s = static_cast<Sample*>(samples);
+  std::sort(s, s + count, [](const Sample& a, const Sample& b) { return sample_less(a, b); });
+}
+
+int b2s_host_select_splitters(void* samples, size_t count, int nranks, void* splitters_out)
+{
+  if (samples == nullptr || splitters_out == nullptr || nranks < 1) return B2S_ERR_INVALID_ARG;
+  Sample* s   = static_cast<Sample*>(samples);
+  Sample* out = static_cast<Sample*>(splitters_out);
+  b2s_host_sort_samples(s, count);
+  long long populated = 0;
+  while ((size_t)populated < count && s[populated].valid) ++populated;
+  for (int k = 1; k < nranks; ++k) {
+    if (populated == 0) {
+      out[k - 1] = Sample{~0ull, 0, 0, 0};
+    } else {
+      out[k - 1] = s[splitter_index(k, populated, nranks)];
+    }
+  }
+  return B2S_OK;
+}
+
+long long b2s_host_sample_position(long long j, long long s, long long n) { return sample_position(j, s, n); }
+
+long long b2s_host_cut_position(const void* splitter, int my_rank, long long lower, long long upper)
+{
+  return cut_position(*static_cast<const Sample*>(splitter), my_rank, lower, upper);
+}
+
+int b2s_samples_per_rank(void) { return SAMPLES_PER_RANK; }
+
+int b2s_kway_merge_workspace_bytes(size_t total, int nruns, size_t* bytes)
+{
+  if (bytes == nullptr || nruns < 1 || nruns > MERGE_MAX_RUNS) return B2S_ERR_INVALID_ARG;
+  const size_t ntiles = (total + MERGE_TILE - 1) / MERGE_TILE;
+  *bytes              = align_up(sizeof(long long) * (ntiles + 1) * nruns, 256);
+  return B2S_OK;
+}
+
+int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int64_t* const* run_idx,
+                   const size_t* run_len, void* out, void* ws, size_t ws_bytes, void* cuda_stream)
+{
+  int xf       = 0;
+  const int kb = kb_of(dtype, &xf);
+  if (kb == 0) return B2S_ERR_UNSUPPORTED;
+  if (nruns < 1 || nruns > MERGE_MAX_RUNS || run_keys == nullptr || run_len == nullptr) return B2S_ERR_INVALID_ARG;
+  MergeRuns runs{};
+  runs.nruns      = nruns;
+  long long total = 0;
+  for (int i = 0; i < nruns; ++i) {
+    runs.keys[i] = run_keys[i];
+    runs.idx[i]  = run_idx ? run_idx[i] : nullptr;
+    runs.len[i]  = (long long)run_len[i];
+    if (run_len[i] > 0 && (run_keys[i] == nullptr || (run_idx && run_idx[i] == nullptr))) return B2S_ERR_INVALID_ARG;
+    total += runs.len[i];
+  }
+  if (total == 0) return B2S_OK;
+  size_t need = 0;
+  b2s_kway_merge_workspace_bytes((size_t)total, nruns, &need);
+  if (out == nullptr) return B2S_ERR_INVALID_ARG;
+  if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 7u)) return B2S_ERR_WORKSPACE;
+  return merge_runs(kb, xf, runs, total, run_idx != nullptr, out, static_cast<long long*>(ws),
+                    static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b2s_nccl_unique_id(void* out128)
+{
+  static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+  if (out128 == nullptr) return B2S_ERR_INVALID_ARG;
+  CK_NCCL(ncclGetUniqueId(static_cast<ncclUniqueId*>(out128)));
+  return B2S_OK;
+}
+
+int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank)
+{
+  if (comm == nullptr || id128 == nullptr) return B2S_ERR_INVALID_ARG;
+  ncclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  ncclComm_t c;
+  CK_NCCL(ncclCommInitRank(&c, nranks, id, rank));
+  *comm = c;
+  return B2S_OK;
+}
+
+int b2s_nccl_comm_destroy(void* comm)
+{
+  if (comm == nullptr) return B2S_OK;
+  CK_NCCL(ncclCommDestroy(static_cast<ncclComm_t>(comm)));
+  return B2S_OK;
+}
+
+int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
+                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                     void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
+                     size_t* out_len, void* cuda_stream)
+{
+  int xf       = 0;
+  const int kb = kb_of(dtype, &xf);
+  if (kb == 0) return B2S_ERR_UNSUPPORTED;
+  if (alloc == nullptr || out_ptr == nullptr || out_len == nullptr || nranks < 1 || rank < 0 || rank >= nranks)
+    return B2S_ERR_INVALID_ARG;
+  if (nranks > MERGE_MAX_RUNS) return B2S_ERR_UNSUPPORTED;
+  if (nranks > 1 && nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
+  if (n_local > 0 && keys_in == nullptr) return B2S_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  ncclComm_t comm     = static_cast<ncclComm_t>(nccl_comm);
+  Scratch mem{alloc, release, alloc_ctx, {}};
+  const long long n = (long long)n_local;
+
+  // ---- 1. local sort; indices are global positions (sort.cu:1851-1854) ----
+  void* keys   = mem.get((size_t)n * kb);
+  int64_t* idx = argsort ? static_cast<int64_t*>(mem.get((size_t)n * 8)) : nullptr;
+  if (keys == nullptr || (argsort && idx == nullptr)) return B2S_ERR_WORKSPACE;
+  if (n > 0) {
+    size_t ws_bytes = 0;
+    int rc = b2s_workspace_bytes(dtype, n_local, n_local, argsort, &ws_bytes);
+    if (rc != B2S_OK) return rc;
+    void* ws = mem.get(ws_bytes);
+    if (ws == nullptr) return B2S_ERR_WORKSPACE;
+    rc = b2s_local_sort(dtype, keys_in, keys, idx, n_local, n_local, global_offset, 1, 1, ws, ws_bytes, stream);
+    if (rc != B2S_OK) return rc;
+    if (nranks == 1) {
+      rc = b2s_check_status(ws, stream);
+      if (rc != B2S_OK) return rc;
+    }
+    // the workspace is released after the exchange below has synchronised the stream
+    if (nranks == 1) mem.drop(ws);
+  }
+  if (nranks == 1) {
+    void* result = argsort ? static_cast<void*>(idx) : keys;
+    mem.disown(result);
+    *out_ptr = result;
+    *out_len = n_local;
+    return B2S_OK;
+  }
+
+  // ---- 2. samples: all-gather, order on the host, pick nranks-1 splitters ----
+  const int s        = SAMPLES_PER_RANK;
+  Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
+  Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nranks));
+  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nranks + 1)));
+  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * nranks));
+  if (!d_samples || !d_split || !d_cuts || !d_count) return B2S_ERR_WORKSPACE;
+  {
+    prof::Scope ps(prof::K_DIST, stream);
+    by_width(kb, [&](auto w) {
+      sample_kernel<decltype(w)::value><<<(s + 127) / 128, 128, 0, stream>>>(keys, n, s, rank, xf, d_samples + (size_t)rank * s);
+      return cudaSuccess;
+    });
+  }
+  CK_CUDA(cudaGetLastError());
+  if (barrier) barrier(barrier_ctx);
+  CK_NCCL(ncclAllGather(d_samples + (size_t)rank * s, d_samples, sizeof(Sample) * s, ncclUint8, comm, stream));
+  if (barrier) barrier(barrier_ctx);
+  std::vector<Sample> h_samples((size_t)s * nranks), h_split(nranks);
+  CK_CUDA(cudaMemcpyAsync(h_samples.data(), d_samples, sizeof(Sample) * s * nranks, cudaMemcpyDeviceToHost, stream));
+  CK_CUDA(cudaStreamSynchronize(stream));
+  b2s_host_select_splitters(h_samples.data(), h_samples.size(), nranks, h_split.data());
+  CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nranks - 1), cudaMemcpyHostToDevice, stream));
+
+  // ---- 3. where the splitters cut my data; exchange the counts ----
+  {
+    prof::Scope ps(prof::K_DIST, stream);
+    by_width(kb, [&](auto w) {
+      cut_kernel<decltype(w)::value><<<(nranks + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nranks, rank, xf, d_cuts);
+      return cudaSuccess;
+    });
+  }
+  CK_CUDA(cudaGetLastError());
+  std::vector<long long> h_cuts(nranks + 1), h_count((size_t)nranks * nranks);
+  CK_CUDA(cudaMemcpyAsync(h_cuts.data(), d_cuts, sizeof(long long) * (nranks + 1), cudaMemcpyDeviceToHost, stream));
+  CK_CUDA(cudaStreamSynchronize(stream));
+  std::vector<long long> send(nranks);
+  for (int p = 0; p < nranks; ++p) send[p] = h_cuts[p + 1] - h_cuts[p];
+  CK_CUDA(cudaMemcpyAsync(d_count + (size_t)rank * nranks, send.data(), sizeof(long long) * nranks, cudaMemcpyHostToDevice, stream));
+  if (barrier) barrier(barrier_ctx);
+  CK_NCCL(ncclAllGather(d_count + (size_t)rank * nranks, d_count, sizeof(long long) * nranks, ncclUint8, comm, stream));
+  if (barrier) barrier(barrier_ctx);
+  CK_CUDA(cudaMemcpyAsync(h_count.data(), d_count, sizeof(long long) * nranks * nranks, cudaMemcpyDeviceToHost, stream));
+  CK_CUDA(cudaStreamSynchronize(stream));
+  for (long long c : h_count)
+    if (c < 0) return B2S_ERR_INVALID_ARG;  // a rank disagreed about the protocol
+
+  // ---- 4. exchange: my slice [cuts[p], cuts[p+1]) goes to rank p; runs arrive in rank order ----
+  MergeRuns runs{};
+  runs.nruns        = nranks;
+  long long total   = 0;
+  std::vector<long long> recv_off(nranks);
+  for (int p = 0; p < nranks; ++p) {
+    recv_off[p] = total;
+    runs.len[p] = h_count[(size_t)p * nranks + rank];
+    total += runs.len[p];
+  }
+  unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)total * kb));
+  int64_t* r_idx        = argsort ? static_cast<int64_t*>(mem.get((size_t)total * 8)) : nullptr;
+  if (r_keys == nullptr || (argsort && r_idx == nullptr)) return B2S_ERR_WORKSPACE;
+  for (int p = 0; p < nranks; ++p) {
+    runs.keys[p] = r_keys + (size_t)recv_off[p] * kb;
+    runs.idx[p]  = argsort ? r_idx + recv_off[p] : nullptr;
+  }
+  const unsigned char* k_bytes = static_cast<const unsigned char*>(keys);
+  if (barrier) barrier(barrier_ctx);
+  CK_NCCL(ncclGroupStart());
+  for (int p = 0; p < nranks; ++p) {
+    if (p == rank) continue;
+    if (send[p] > 0) {
+      CK_NCCL(ncclSend(k_bytes + (size_t)h_cuts[p] * kb, (size_t)send[p] * kb, ncclUint8, p, comm, stream));
+      if (argsort) CK_NCCL(ncclSend(idx + h_cuts[p], (size_t)send[p], ncclInt64, p, comm, stream));
+    }
+    if (runs.len[p] > 0) {
+      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[p] * kb, (size_t)runs.len[p] * kb, ncclUint8, p, comm, stream));
+      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[p], (size_t)runs.len[p], ncclInt64, p, comm, stream));
+    }
+  }
+  CK_NCCL(ncclGroupEnd());
+  if (barrier) barrier(barrier_ctx);
+  if (send[rank] > 0) {  // my own slice stays on this GPU
+    CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[rank] * kb, k_bytes + (size_t)h_cuts[rank] * kb,
+                            (size_t)send[rank] * kb, cudaMemcpyDeviceToDevice, stream));
+    if (argsort)
+      CK_CUDA(cudaMemcpyAsync(r_idx + recv_off[rank], idx + h_cuts[rank], (size_t)send[rank] * 8,
+                              cudaMemcpyDeviceToDevice, stream));
+  }
+
+  // ---- 5. stable k-way merge in rank order ----
+  void* result = mem.get((size_t)total * (argsort ? 8 : kb));
+  if (result == nullptr) return B2S_ERR_WORKSPACE;
+  if (total > 0) {
+    size_t mws = 0;
+    b2s_kway_merge_workspace_bytes((size_t)total, nranks, &mws);
+    void* d_tcuts = mem.get(mws);
+    if (d_tcuts == nullptr) return B2S_ERR_WORKSPACE;
+    int rc = merge_runs(kb, xf, runs, total, argsort != 0, result, static_cast<long long*>(d_tcuts), stream);
+    if (rc != B2S_OK) return rc;
+  }
+  // temporaries are handed back only once the stream is done with them
+  CK_CUDA(cudaStreamSynchronize(stream));
+  mem.disown(result);
+  *out_ptr = result;
+  *out_len = (size_t)total;
+  return B2S_OK;
+}
+}

@@ -1,0 +1,220 @@
+// Stable k-way merge of the sorted runs a rank receives in the exchange (one run per source
+// rank, in rank order): one pass over the data instead of the reference's log2(P) sweeps of
+// pairwise thrust::merge (src/cupynumeric/sort/sort.cu:608-790).
+//
+// Kernel A finds, for every output tile boundary, where that boundary cuts each run (one warp
+// per boundary, one lane per run, bisection on the key value).  Kernel B loads a tile's pieces
+// into shared memory and merges them there with a tree of pairwise merge-path merges.
+#pragma once
+#include "b2s_common.cuh"
+
+namespace b2s {
+
+constexpr int MERGE_MAX_RUNS = 32;
+constexpr int MERGE_THREADS  = 256;
+constexpr int MERGE_VT       = 8;
+constexpr int MERGE_TILE     = MERGE_THREADS * MERGE_VT;
+
+struct MergeRuns {
+  const void* keys[MERGE_MAX_RUNS];     // run i: len[i] sorted keys
+  const int64_t* idx[MERGE_MAX_RUNS];   // payload of run i (argsort) or null
+  long long len[MERGE_MAX_RUNS];
+  int nruns;
+};
+
+template <int KB>
+__device__ __forceinline__ unsigned long long okey_at(const void* base, long long i, int xf)
+{
+  using K = typename KeyOf<KB>::type;
+  return (unsigned long long)to_ordered_rt<KB>(static_cast<const K*>(base)[i], xf);
+}
+
+// first position in [lo, hi) of run whose ordered key is >= x
+template <int KB>
+__device__ __forceinline__ long long lower_bound_okey(const void* base, long long lo, long long hi,
+                                                      unsigned long long x, int xf)
+{
+  while (lo < hi) {
+    const long long mid = lo + ((hi - lo) >> 1);
+    if (okey_at<KB>(base, mid, xf) < x) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// cuts[b * nruns + i] = number of elements of run i among the first b * MERGE_TILE elements of
+// the stable merge; b = 0 .. ntiles.
+template <int KB>
+__global__ void __launch_bounds__(256)
+merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf, long long* __restrict__ cuts)
+{
+  const int lane          = threadIdx.x & 31;
+  const long long b       = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (b > ntiles) return;
+  const int nruns         = runs.nruns;
+  const bool mine         = lane < nruns;
+  const long long n_i     = mine ? runs.len[lane] : 0;
+  const void* base        = mine ? runs.keys[lane] : nullptr;
+  long long r             = b * MERGE_TILE;
+  if (r > total) r = total;
+  long long cut;
+  if (r == 0) {
+    cut = 0;
+  } else if (r == total) {
+    cut = n_i;
+  } else {
+    // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit.
+    constexpr int BITS = 8 * KB;
+    unsigned long long x = 0;
+    long long lo = 0, hi = n_i;  // lower_bound of every future candidate lies in [lo, hi]
+    for (int bit = BITS - 1; bit >= 0; --bit) {
+      const unsigned long long cand = x | (1ull << bit);
+      const long long p = lower_bound_okey<KB>(base, lo, hi, cand, xf);
+      long long less = p;
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) less += __shfl_xor_sync(0xFFFFFFFFu, less, s);
+      if (less <= r) {
+        x  = cand;
+        lo = p;
+      } else {
+        hi = p;
+      }
+    }
+    // lo = #(keys < v) in this run; ties (== v) are handed out in run order
+    const long long lower = lo;
+    long long upper       = n_i;
+    if (x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1))) upper = lower_bound_okey<KB>(base, lo, n_i, x + 1, xf);
+    long long less_total = lower;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) less_total += __shfl_xor_sync(0xFFFFFFFFu, less_total, s);
+    const long long equal = upper - lower;
+    long long incl        = equal;  // inclusive prefix of `equal` over lanes
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+      const long long t = __shfl_up_sync(0xFFFFFFFFu, incl, s);
+      if (lane >= s) incl += t;
+    }
+    long long take = (r - less_total) - (incl - equal);  // ties left for this run
+    take           = take < 0 ? 0 : (take > equal ? equal : take);
+    cut            = lower + take;
+  }
+  if (mine) cuts[b * nruns + lane] = cut;
+}
+
+template <int KB, bool ARGS>
+struct MergeSmem {
+  static constexpr size_t OFF_RAW  = 0;
+  static constexpr size_t OFF_IDX_RAW = OFF_RAW + (size_t)MERGE_TILE * KB;
+  static constexpr size_t OFF_IDX  = (OFF_IDX_RAW + 15) / 16 * 16;
+  static constexpr size_t OFF_OK0  = OFF_IDX + (ARGS ? (size_t)MERGE_TILE * 8 : 0);
+  static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_TILE * 8;
+  static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_TILE * 8;
+  static constexpr size_t OFF_SL1  = OFF_SL0 + (size_t)MERGE_TILE * 2;
+  static constexpr size_t OFF_BND  = OFF_SL1 + (size_t)MERGE_TILE * 2;
+  static constexpr size_t OFF_SRC  = (OFF_BND + (MERGE_MAX_RUNS + 1) * 4 + 15) / 16 * 16;  // 8-byte entries
+  static constexpr size_t BYTES    = OFF_SRC + MERGE_MAX_RUNS * 8;
+};
+
+// One CTA per output tile.  ARGS: emit the int64 payload (argsort); else emit the keys.
+template <int KB, bool ARGS>
+__global__ void __launch_bounds__(MERGE_THREADS)
+merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __restrict__ cuts,
+                   void* __restrict__ out)
+{
+  using K = typename KeyOf<KB>::type;
+  using S = MergeSmem<KB, ARGS>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  K* raw                    = reinterpret_cast<K*>(smem + S::OFF_RAW);
+  int64_t* pay              = reinterpret_cast<int64_t*>(smem + S::OFF_IDX);
+  unsigned long long* ok[2] = {reinterpret_cast<unsigned long long*>(smem + S::OFF_OK0),
+                               reinterpret_cast<unsigned long long*>(smem + S::OFF_OK1)};
+  unsigned short* sl[2]     = {reinterpret_cast<unsigned short*>(smem + S::OFF_SL0),
+                               reinterpret_cast<unsigned short*>(smem + S::OFF_SL1)};
+  int* bnd                  = reinterpret_cast<int*>(smem + S::OFF_BND);       // piece starts in the tile
+  long long* src0           = reinterpret_cast<long long*>(smem + S::OFF_SRC); // piece starts in the runs
+
+  const int tid         = threadIdx.x;
+  const long long b     = blockIdx.x;
+  const int nruns       = runs.nruns;
+  const long long base  = b * MERGE_TILE;
+  const int count       = (int)((total - base) < MERGE_TILE ? (total - base) : MERGE_TILE);
+  int p2 = 1;
+  while (p2 < nruns) p2 <<= 1;  // tree width
+
+  if (tid == 0) {
+    int off = 0;
+    for (int i = 0; i < nruns; ++i) {
+      const long long c0 = cuts[b * nruns + i], c1 = cuts[(b + 1) * nruns + i];
+      bnd[i]  = off;
+      src0[i] = c0;
+      off += (int)(c1 - c0);
+    }
+    for (int i = nruns; i <= p2; ++i) bnd[i] = off;  // padding runs are empty
+  }
+  __syncthreads();
+
+  // load the pieces, in run order
+  for (int q = tid; q < count; q += MERGE_THREADS) {
+    int i = 0;
+    while (i + 1 < nruns && bnd[i + 1] <= q) ++i;
+    const long long s = src0[i] + (q - bnd[i]);
+    const K k         = static_cast<const K*>(runs.keys[i])[s];
+    raw[q]            = k;
+    if (ARGS) pay[q] = runs.idx[i][s];
+    ok[0][q] = (unsigned long long)to_ordered_rt<KB>(k, xf);
+    sl[0][q] = (unsigned short)q;
+  }
+  __syncthreads();
+
+  // tree of pairwise stable merges; ties take from the lower run first
+  int cur = 0;
+  for (int g = 2; g <= p2; g <<= 1) {
+    const unsigned long long* ik = ok[cur];
+    const unsigned short* is     = sl[cur];
+    unsigned long long* okd      = ok[cur ^ 1];
+    unsigned short* sld          = sl[cur ^ 1];
+    int q        = tid * MERGE_VT;
+    const int q1 = min(q + MERGE_VT, count);
+    int pair     = 0;
+    while (q < q1) {
+      while (bnd[(pair + 1) * g] <= q) ++pair;  // pair whose output span holds q
+      const int s0 = bnd[pair * g], mid = bnd[pair * g + g / 2], s1 = bnd[(pair + 1) * g];
+      const int na = mid - s0, nb = s1 - mid;
+      const int end = min(q1, s1);
+      const int diag = q - s0;
+      int lo = max(0, diag - nb), hi = min(diag, na);
+      while (lo < hi) {
+        const int m = (lo + hi) >> 1;
+        if (ik[s0 + m] <= ik[mid + diag - 1 - m]) lo = m + 1; else hi = m;
+      }
+      int ia = lo, ib = diag - lo;
+      unsigned long long ka = ia < na ? ik[s0 + ia] : 0, kb = ib < nb ? ik[mid + ib] : 0;
+      for (; q < end; ++q) {
+        const bool take_a = (ib >= nb) || (ia < na && ka <= kb);
+        if (take_a) {
+          okd[q] = ka;
+          sld[q] = is[s0 + ia];
+          ++ia;
+          ka = ia < na ? ik[s0 + ia] : 0;
+        } else {
+          okd[q] = kb;
+          sld[q] = is[mid + ib];
+          ++ib;
+          kb = ib < nb ? ik[mid + ib] : 0;
+        }
+      }
+    }
+    cur ^= 1;
+    __syncthreads();
+  }
+
+  const unsigned short* fs = sl[cur];
+  if (ARGS) {
+    int64_t* o = static_cast<int64_t*>(out) + base;
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[fs[q]];
+  } else {
+    K* o = static_cast<K*>(out) + base;
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[fs[q]];
+  }
+}
+
+}  // namespace b2s

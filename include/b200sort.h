@@ -96,6 +96,64 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
  * CUPYNUMERIC_CHECK_CUDA_STREAM (src/cupynumeric/cuda_help.h:291-302). */
 int b2s_check_status(void* ws, void* cuda_stream);
 
+/* ---- distributed 1-D sort ------------------------------------------------------------------- */
+
+/* Device memory from the caller's pool, 256-byte aligned, valid on the current device; NULL on
+ * failure.  Role of legate::create_buffer<T>(n, Memory::GPU_FB_MEM) in the reference
+ * (src/cupynumeric/sort/sort.cu:1833-1869). */
+typedef void* (*b2s_alloc_fn)(void* ctx, size_t bytes);
+/* Returns memory obtained from the paired b2s_alloc_fn (Buffer::destroy(), sort.cu:1933-1936). */
+typedef void (*b2s_free_fn)(void* ctx, void* ptr);
+/* Optional host barrier among the point tasks of one launch, called around every NCCL call
+ * like context.concurrent_task_barrier() (sort.cu:1313-1315,1393,1412,1511,1530,1686,1734).
+ * May be NULL when each rank is a process of its own. */
+typedef void (*b2s_barrier_fn)(void* ctx);
+
+/* Sorts a 1-D array whose contiguous tiles live on the `nranks` GPUs of one communicator: rank
+ * r holds `n_local` elements starting at global position `global_offset`.  Every rank of the
+ * communicator must call, even with n_local == 0 (src/cupynumeric/sort/sort_template.inl:62-72).
+ * On return *out_ptr is a buffer from `alloc` holding *out_len elements - this rank's part of
+ * the globally sorted values, or (argsort) of their int64 global indices; the parts of ranks
+ * 0..nranks-1, concatenated, are the global stable sort.  The buffer belongs to the caller, as
+ * with an unbound store's bind_data (sort.cu:1774-1783).  Synchronises the stream.
+ * Replaces SortImplBody<GPU> for unbound 1-D outputs plus sample_sort_nccl_nd
+ * (src/cupynumeric/sort/sort.cu:1797-1940 and 1270-1784). */
+int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
+                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                     void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
+                     size_t* out_len, void* cuda_stream);
+
+/* Stable merge of `nruns` (<= 32) sorted runs, ties taken from the lower-numbered run first:
+ * out receives the merged keys, or - when run_idx is not NULL - only the merged int64 payloads.
+ * `ws`: b2s_kway_merge_workspace_bytes(total, nruns) bytes of device scratch.  This is the last
+ * step of b2s_dist_sort_1d, exported on its own; it replaces merge_all_buffers
+ * (src/cupynumeric/sort/sort.cu:608-790). */
+int b2s_kway_merge_workspace_bytes(size_t total, int nruns, size_t* bytes);
+int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int64_t* const* run_idx,
+                   const size_t* run_len, void* out, void* ws, size_t ws_bytes, void* cuda_stream);
+
+/* NCCL communicator plumbing for hosts that are not Legate (which hands the task its
+ * communicator: cupynumeric/_thunk/_sort.py:89-90, sort.cu:1923).  `id128` is the 128-byte
+ * ncclUniqueId made on one rank and distributed by the caller. */
+int b2s_nccl_unique_id(void* out128);
+int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank);
+int b2s_nccl_comm_destroy(void* comm);
+
+/* Host-side pieces of the splitter logic, exported so that they can be exercised without a GPU.
+ * A sample is the 24-byte record {uint64 ordered_key; int64 position; int32 rank; int32 valid}
+ * (role of SegmentSample, src/cupynumeric/sort/sort.h:37-43). */
+int b2s_samples_per_rank(void);
+/* Position of regular sample j of s in n >= s sorted elements (sort.cu:523-527). */
+long long b2s_host_sample_position(long long j, long long s, long long n);
+/* Orders `count` samples by (ordered_key, rank, position), unpopulated ones last
+ * (SegmentSampleComparator, sort.h:60-81; thrust::stable_sort at sort.cu:1441-1445). */
+void b2s_host_sort_samples(void* samples, size_t count);
+/* Sorts the gathered samples and writes the nranks-1 splitters (sort.cu:1455-1470). */
+int b2s_host_select_splitters(void* samples, size_t count, int nranks, void* splitters_out);
+/* How many leading elements of rank my_rank's sorted data go left of the splitter, given the
+ * counts of local keys below / not above the splitter's key (sort.cu:170-187). */
+long long b2s_host_cut_position(const void* splitter, int my_rank, long long lower, long long upper);
+
 /* ---- measurement aids (no counterpart in the reference, which relies on Legate's profiler,
  * cupynumeric/_utils/profiling.py:33-73) ------------------------------------------------------ */
 

@@ -1,0 +1,58 @@
+"""Child process of the multi-GPU test: one rank of a distributed sort through the public API,
+checked against the oracle on rank 0.  Launched with torch.distributed.run."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    workload = sys.argv[1]
+    n = int(sys.argv[2]) if len(sys.argv) > 2 else 1 << 20
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    import cupynumeric_b200 as num
+    from cupynumeric_b200 import workloads as w
+    from cupynumeric_b200._dist import destroy_comm
+
+    if workload == "c4":
+        shard, argsort = w.c4_int64_zipf_shard(n, rank), False
+    elif workload == "c5":
+        shard, argsort = w.c5_uint64_nearly_sorted_shard(n, rank, world), True
+    else:
+        shard, argsort = w.c2_float32_nan_dups(n, seed=202 + rank), True
+    if rank == world - 1 and workload == "c4":
+        shard = shard[: n // 3]  # ragged tiles
+    lens = [None] * world
+    dist.all_gather_object(lens, int(shard.size))
+    lo = sum(lens[:rank])
+    arr = num.array(shard, global_lo=lo)
+    res = num.argsort(arr, kind="stable") if argsort else num.sort(arr)
+    part = res.to_numpy()
+    parts, shards, starts = [None] * world, [None] * world, [None] * world
+    dist.all_gather_object(parts, part)
+    dist.all_gather_object(shards, shard)
+    dist.all_gather_object(starts, res.global_lo)
+    if rank == 0:
+        whole = np.concatenate(shards)
+        got = np.concatenate(parts)
+        want = np.argsort(whole, kind="stable") if argsort else np.sort(whole, kind="stable")
+        assert got.shape == want.shape, (got.shape, want.shape)
+        same = np.array_equal(got, want) if argsort else np.array_equal(got.view(np.uint8), want.view(np.uint8))
+        assert same, "distributed result differs from the global stable sort"
+        assert starts == [int(x) for x in np.cumsum([0] + [len(p) for p in parts])[:-1]], starts
+        sizes = [len(p) for p in parts]
+        assert max(sizes) <= 1.2 * sum(sizes) / world + 16, sizes
+        print("DIST_OK", workload, sizes)
+    destroy_comm()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

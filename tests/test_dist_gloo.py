@@ -1,0 +1,138 @@
+"""World-size-2 CPU test of the distributed sort's host logic over the gloo backend: regular
+sampling, splitter selection and the cut rule come from the C ABI's host entry points; the local
+sort and the final merge are played by the oracle, the exchange by gloo.  Checks that the
+rank-ordered concatenation is the global stable sort, that indices are global, and that the
+splitters balance heavy duplicates."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def ordered_u64(a: np.ndarray) -> np.ndarray:
+    """Order-preserving unsigned image of int64 / uint64 keys (what the library samples)."""
+    if a.dtype == np.int64:
+        return (a.view(np.uint64) ^ np.uint64(1 << 63))
+    return a.astype(np.uint64)
+
+
+def make_shard(kind: str, rank: int, n: int) -> np.ndarray:
+    from cupynumeric_b200 import workloads as w
+
+    if kind == "zipf":
+        return w.c4_int64_zipf_shard(n, rank)
+    if kind == "nearly_sorted":
+        return w.c5_uint64_nearly_sorted_shard(n, rank, 2)
+    if kind == "all_equal":
+        return np.full(n, 7, dtype=np.int64)
+    if kind == "one_empty":
+        return np.arange(n, 0, -1, dtype=np.int64) if rank == 0 else np.empty(0, dtype=np.int64)
+    raise ValueError(kind)
+
+
+def worker(rank: int, world: int, port: int, kind: str, n: int, argsort: bool, ret):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cupynumeric_b200 import _lib
+        from oracle import np_task_sort
+
+        lib = _lib.lib()
+        shard = make_shard(kind, rank, n)
+        n_local = shard.size
+        lens = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(lens, torch.tensor([n_local]))
+        global_lo = int(sum(int(x) for x in lens[:rank]))
+
+        # local sort (oracle) with global indices
+        order = np_task_sort(shard, max(n_local, 1), True) if n_local else np.empty(0, np.int64)
+        keys = shard[order]
+        idx = order + global_lo
+        okeys = ordered_u64(keys)
+
+        # regular samples, exactly as the device kernel takes them
+        s = lib.b2s_samples_per_rank()
+        mine = np.zeros(s, dtype=_lib.SAMPLE_DTYPE)
+        s_eff = min(s, n_local)
+        for j in range(s):
+            if j < s_eff:
+                p = lib.b2s_host_sample_position(j, s_eff, n_local)
+                mine[j] = (okeys[p], p, rank, 1)
+            else:
+                mine[j] = (np.uint64(2**64 - 1), 0, rank, 0)
+        gathered = [torch.zeros(mine.nbytes, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(mine.view(np.uint8)))
+        samples = np.concatenate([g.numpy() for g in gathered]).view(_lib.SAMPLE_DTYPE).copy()
+        splitters = np.zeros(world - 1, dtype=_lib.SAMPLE_DTYPE)
+        assert lib.b2s_host_select_splitters(samples.ctypes.data, samples.size, world, splitters.ctypes.data) == 0
+
+        cuts = [0]
+        for k in range(world - 1):
+            sp = splitters[k:k + 1]
+            if not sp["valid"][0]:
+                cuts.append(n_local)
+                continue
+            lower = int(np.searchsorted(okeys, sp["okey"][0], side="left"))
+            upper = int(np.searchsorted(okeys, sp["okey"][0], side="right"))
+            cuts.append(int(lib.b2s_host_cut_position(sp.ctypes.data, rank, lower, upper)))
+        cuts.append(n_local)
+        assert all(a <= b for a, b in zip(cuts, cuts[1:])), cuts
+
+        # exchange
+        send_counts = torch.tensor([cuts[p + 1] - cuts[p] for p in range(world)])
+        recv_counts = torch.zeros(world, dtype=torch.int64)
+        dist.all_to_all_single(recv_counts, send_counts)
+        payload = idx if argsort else keys.view(np.int64)
+        recv_k = torch.zeros(int(recv_counts.sum()), dtype=torch.int64)
+        recv_p = torch.zeros(int(recv_counts.sum()), dtype=torch.int64)
+        dist.all_to_all_single(recv_k, torch.from_numpy(np.ascontiguousarray(keys.view(np.int64))),
+                               recv_counts.tolist(), send_counts.tolist())
+        dist.all_to_all_single(recv_p, torch.from_numpy(np.ascontiguousarray(payload)),
+                               recv_counts.tolist(), send_counts.tolist())
+        rk = recv_k.numpy().view(shard.dtype)
+        # runs arrive in rank order: a stable sort of their concatenation is the stable merge
+        m = np.argsort(rk, kind="stable")
+        part = recv_p.numpy()[m] if argsort else rk[m]
+
+        parts = [None] * world
+        dist.all_gather_object(parts, part)
+        shards = [None] * world
+        dist.all_gather_object(shards, shard)
+        if rank == 0:
+            whole = np.concatenate(shards)
+            got = np.concatenate(parts)
+            want = np.argsort(whole, kind="stable") if argsort else np.sort(whole, kind="stable")
+            ok = bool(np.array_equal(got, want.astype(got.dtype) if argsort else want))
+            sizes = [len(p) for p in parts]
+            ret.put((ok, sizes, whole.size))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind,n,argsort", [("zipf", 20000, False), ("zipf", 20000, True),
+                                           ("nearly_sorted", 16384, True), ("all_equal", 5000, True),
+                                           ("one_empty", 3000, False), ("zipf", 100, True)])
+def test_two_rank_sample_sort_over_gloo(kind, n, argsort):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = 29500 + (os.getpid() + hash((kind, n, argsort))) % 2000
+    procs = [ctx.Process(target=worker, args=(r, 2, port, kind, n, argsort, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    ok, sizes, total = ret.get(timeout=10)
+    assert ok, "rank-ordered concatenation differs from the global stable sort"
+    assert sum(sizes) == total
+    if kind in ("zipf", "all_equal", "nearly_sorted") and total >= 5000:
+        # (rank, position) tie-breaking keeps the parts balanced even when one key dominates
+        assert max(sizes) <= 0.55 * total, sizes
