@@ -80,19 +80,15 @@ def dist_sort_1d(tile: torch.Tensor, argsort: bool, global_lo: int):
     assert tile.is_cuda and tile.ndim == 1 and tile.is_contiguous()
     np_dtype = to_numpy_dtype(tile.dtype)
     pool = _Pool()
-    out_ptr, out_len = ctypes.c_void_p(), ctypes.c_size_t()
+    out_ptr, out_len, out_start = ctypes.c_void_p(), ctypes.c_size_t(), ctypes.c_int64()
     st = lib.b2s_dist_sort_1d(_lib.DTYPE_CODE[np_dtype], tile.data_ptr(), tile.numel(), int(global_lo), int(argsort),
                               nccl_comm(), dist.get_rank(), dist.get_world_size(),
                               ctypes.cast(pool.alloc_cb, ctypes.c_void_p), ctypes.cast(pool.free_cb, ctypes.c_void_p),
                               None, None, None, ctypes.byref(out_ptr), ctypes.byref(out_len),
-                              runtime.stream_handle())
+                              ctypes.byref(out_start), runtime.stream_handle())
     _lib.check(st, "b2s_dist_sort_1d")
     raw = pool.adopt(out_ptr.value)
     res_dtype = torch.int64 if argsort else tile.dtype
     n = out_len.value
     result = raw[: n * res_dtype.itemsize].view(res_dtype)
-    # where this part starts in the global result: exclusive sum of the lengths of lower ranks
-    lens = [torch.zeros(1, dtype=torch.int64, device=tile.device) for _ in range(dist.get_world_size())]
-    dist.all_gather(lens, torch.tensor([n], dtype=torch.int64, device=tile.device))
-    start = int(sum(int(x.item()) for x in lens[: dist.get_rank()]))
-    return result, start
+    return result, int(out_start.value)

@@ -258,7 +258,7 @@ int b2s_nccl_comm_destroy(void* comm)
 int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
                      void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
                      void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
-                     size_t* out_len, void* cuda_stream)
+                     size_t* out_len, int64_t* out_global_offset, void* cuda_stream)
 {
   int xf       = 0;
   const int kb = kb_of(dtype, &xf);
@@ -297,6 +297,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     mem.disown(result);
     *out_ptr = result;
     *out_len = n_local;
+    if (out_global_offset) *out_global_offset = 0;
     return B2S_OK;
   }
 
@@ -404,6 +405,12 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   mem.disown(result);
   *out_ptr = result;
   *out_len = (size_t)total;
+  if (out_global_offset) {
+    long long before = 0;  // elements that end up on lower ranks
+    for (int d = 0; d < rank; ++d)
+      for (int src = 0; src < nranks; ++src) before += h_count[(size_t)src * nranks + d];
+    *out_global_offset = before;
+  }
   return B2S_OK;
 }
 }

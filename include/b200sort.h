@@ -115,13 +115,14 @@ typedef void (*b2s_barrier_fn)(void* ctx);
  * On return *out_ptr is a buffer from `alloc` holding *out_len elements - this rank's part of
  * the globally sorted values, or (argsort) of their int64 global indices; the parts of ranks
  * 0..nranks-1, concatenated, are the global stable sort.  The buffer belongs to the caller, as
- * with an unbound store's bind_data (sort.cu:1774-1783).  Synchronises the stream.
+ * with an unbound store's bind_data (sort.cu:1774-1783); *out_global_offset (may be NULL) is the
+ * global position of its first element.  Synchronises the stream.
  * Replaces SortImplBody<GPU> for unbound 1-D outputs plus sample_sort_nccl_nd
  * (src/cupynumeric/sort/sort.cu:1797-1940 and 1270-1784). */
 int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
                      void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
                      void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
-                     size_t* out_len, void* cuda_stream);
+                     size_t* out_len, int64_t* out_global_offset, void* cuda_stream);
 
 /* Stable merge of `nruns` (<= 32) sorted runs, ties taken from the lower-numbered run first:
  * out receives the merged keys, or - when run_idx is not NULL - only the merged int64 payloads.

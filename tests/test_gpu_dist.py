@@ -81,7 +81,7 @@ def test_dist_entry_point_single_rank(cuda_device):
         out_ptr, out_len = ctypes.c_void_p(), ctypes.c_size_t()
         st = lib.b2s_dist_sort_1d(_lib.DTYPE_CODE[a.dtype], d.data_ptr(), a.size, 1000, argsort, None, 0, 1,
                                   ctypes.cast(pool.alloc_cb, ctypes.c_void_p), ctypes.cast(pool.free_cb, ctypes.c_void_p),
-                                  None, None, None, ctypes.byref(out_ptr), ctypes.byref(out_len),
+                                  None, None, None, ctypes.byref(out_ptr), ctypes.byref(out_len), None,
                                   torch.cuda.current_stream().cuda_stream)
         _lib.check(st, "dist")
         torch.cuda.synchronize()
