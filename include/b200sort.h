@@ -96,6 +96,21 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
  * CUPYNUMERIC_CHECK_CUDA_STREAM (src/cupynumeric/cuda_help.h:291-302). */
 int b2s_check_status(void* ws, void* cuda_stream);
 
+/* Same contract as b2s_local_sort, for callers that cannot hand over a workspace because they
+ * cannot allocate one: for instance a task body under a runtime that forbids cudaMalloc while
+ * tasks are in flight, or a thread whose memory pool is exhausted.  It has no counterpart in the
+ * reference.  The scratch is a fixed device array of B2S_NOALLOC_SCRATCH_BYTES that each GPU
+ * holds from the moment the library is loaded; the call allocates nothing and returns
+ * B2S_ERR_WORKSPACE when b2s_workspace_bytes(...) for the problem exceeds that size.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call before any stream capture begins.  All calls on a device share the one array:
+ * two calls whose kernels may overlap on the GPU (different streams, no ordering) race with each
+ * other; calls on one stream are safe.  A device-side wait that ran out cannot be read back
+ * through b2s_check_status here. */
+#define B2S_NOALLOC_SCRATCH_BYTES (32u << 20)
+int b2s_local_sort_noalloc(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t volume,
+                           size_t segment, int64_t index_offset, int ndim_is_1, void* cuda_stream);
+
 /* ---- distributed 1-D sort ------------------------------------------------------------------- */
 
 /* Device memory from the caller's pool, 256-byte aligned, valid on the current device; NULL on
