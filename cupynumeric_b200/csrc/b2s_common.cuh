@@ -192,13 +192,24 @@ __device__ __forceinline__ unsigned int lanemask_lt()
 #ifndef B2S_RANK_MATCH
 #define B2S_RANK_MATCH 0
 #endif
+#ifndef B2S_BALLOT_FORM
+#define B2S_BALLOT_FORM 0
+#endif
 template <int B>
 __device__ __forceinline__ void ballot_step(unsigned int d, unsigned int& differs)
 {
+#if B2S_BALLOT_FORM == 1
+  // test-and-vote form: one logic op with a predicate result, one vote, one select, one logic op
+  const bool bit          = (d & (1u << B)) != 0;
+  const unsigned int bal  = __ballot_sync(0xFFFFFFFFu, bit);
+  const unsigned int mine = bit ? 0xFFFFFFFFu : 0u;
+  differs |= bal ^ mine;
+#else
   // the caller's bit B replicated over a word: 0 or 0xFFFFFFFF
   const int mine         = (int)(d << (31 - B)) >> 31;
   const unsigned int bal = __ballot_sync(0xFFFFFFFFu, mine < 0);
   differs |= bal ^ (unsigned int)mine;
+#endif
 }
 
 __device__ __forceinline__ unsigned int warp_peers(unsigned int d)
@@ -210,6 +221,9 @@ __device__ __forceinline__ unsigned int warp_peers(unsigned int d)
   // the caller's own bit replicated over the word; the peers are the lanes that differ nowhere.
   // The per-bit step is PTX so that it stays a test, a vote and a select.
   unsigned int differs = 0;
+#if B2S_BALLOT_FORM == 1
+  asm volatile("" : "+r"(d));  // keep the digit in a register of its own
+#endif
   ballot_step<0>(d, differs);
   ballot_step<1>(d, differs);
   ballot_step<2>(d, differs);

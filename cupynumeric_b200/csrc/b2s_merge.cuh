@@ -64,9 +64,25 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
   } else {
     // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit.
     constexpr int BITS = 8 * KB;
-    unsigned long long x = 0;
+    // Bits above the highest one in which the smallest and the largest key of all runs differ are
+    // common to every key: start the bisection below them.
+    unsigned long long kmin = ~0ull, kmax = 0;
+    if (n_i > 0) {
+      kmin = okey_at<KB>(base, 0, xf);
+      kmax = okey_at<KB>(base, n_i - 1, xf);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+      const unsigned long long a = __shfl_xor_sync(0xFFFFFFFFu, kmin, s);
+      const unsigned long long c = __shfl_xor_sync(0xFFFFFFFFu, kmax, s);
+      kmin = a < kmin ? a : kmin;
+      kmax = c > kmax ? c : kmax;
+    }
+    const unsigned long long diff = kmin ^ kmax;
+    const int top = diff ? 63 - __clzll((long long)diff) : -1;  // highest varying bit
+    unsigned long long x = top >= 63 ? 0ull : (top < 0 ? kmin : (kmin >> (top + 1)) << (top + 1));
     long long lo = 0, hi = n_i;  // lower_bound of every future candidate lies in [lo, hi]
-    for (int bit = BITS - 1; bit >= 0; --bit) {
+    for (int bit = top < BITS - 1 ? top : BITS - 1; bit >= 0; --bit) {
       const unsigned long long cand = x | (1ull << bit);
       const long long p = lower_bound_okey<KB>(base, lo, hi, cand, xf);
       long long less = p;
