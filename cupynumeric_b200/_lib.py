@@ -27,7 +27,7 @@ DTYPE_CODE = {
 
 B2S_OK = 0
 # b2s_kernel_kind_t
-K_HIST, K_SCAN, K_SWEEP, K_FIXUP, K_SEGSORT, K_UNIT, K_DIST, K_MERGE = range(8)
+K_HIST, K_SCAN, K_SWEEP, K_FIXUP, K_SEGSORT, K_UNIT, K_DIST, K_MERGE, K_XCHG = range(9)
 STATUS_NAMES = {0: "B2S_OK", 1: "B2S_ERR_INVALID_ARG", 2: "B2S_ERR_CUDA", 3: "B2S_ERR_NCCL",
                 4: "B2S_ERR_WORKSPACE", 5: "B2S_ERR_TIMEOUT", 6: "B2S_ERR_UNSUPPORTED"}
 

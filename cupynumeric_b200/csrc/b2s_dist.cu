@@ -6,6 +6,9 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 #include <vector>
@@ -133,8 +136,15 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
     constexpr int KB = decltype(w)::value;
     {
       prof::Scope ps(prof::K_DIST, stream);
+      const long long ncoarse = (ntiles + MERGE_COARSE_STRIDE - 1) / MERGE_COARSE_STRIDE + 1;
+      merge_partition_kernel<KB><<<(unsigned int)((ncoarse + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts,
+                                                                                   MERGE_COARSE_STRIDE, 0);
+    }
+    {
+      prof::Scope ps(prof::K_DIST, stream);
       const long long warps = ntiles + 1;
-      merge_partition_kernel<KB><<<(unsigned int)((warps + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts);
+      merge_partition_kernel<KB><<<(unsigned int)((warps + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts,
+                                                                                 MERGE_COARSE_STRIDE, 1);
     }
     prof::Scope ps(prof::K_MERGE, stream);
     if (args) {
@@ -152,6 +162,25 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
   });
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
+
+// Host-side phase trace of the distributed sort (B2S_DIST_TRACE=1, rank 0 prints).
+struct PhaseTrace {
+  bool on;
+  std::chrono::steady_clock::time_point t0;
+  char line[512];
+  int used = 0;
+  int rk = 0;
+  explicit PhaseTrace(int rank) : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank), t0(std::chrono::steady_clock::now()) {}
+  void mark(const char* what)
+  {
+    if (!on) return;
+    const auto t1 = std::chrono::steady_clock::now();
+    used += std::snprintf(line + used, sizeof(line) - used, " %s=%.2f", what,
+                          std::chrono::duration<double, std::milli>(t1 - t0).count());
+    t0 = t1;
+  }
+  ~PhaseTrace() { if (on) std::fprintf(stderr, "[b2s dist ms r%d]%s\n", rk, line); }
+};
 
 #define CK_CUDA(x) do { if ((x) != cudaSuccess) return B2S_ERR_CUDA; } while (0)
 #define CK_NCCL(x) do { if ((x) != ncclSuccess) return B2S_ERR_NCCL; } while (0)
@@ -272,6 +301,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   ncclComm_t comm     = static_cast<ncclComm_t>(nccl_comm);
   Scratch mem{alloc, release, alloc_ctx, {}};
   const long long n = (long long)n_local;
+  PhaseTrace trace(rank);
 
   // ---- 1. local sort; indices are global positions (sort.cu:1851-1854) ----
   void* keys   = mem.get((size_t)n * kb);
@@ -301,6 +331,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     return B2S_OK;
   }
 
+  trace.mark("enqueue_local_sort");
   // ---- 2. samples: all-gather, order on the host, pick nranks-1 splitters ----
   const int s        = SAMPLES_PER_RANK;
   Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
@@ -322,6 +353,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   std::vector<Sample> h_samples((size_t)s * nranks), h_split(nranks);
   CK_CUDA(cudaMemcpyAsync(h_samples.data(), d_samples, sizeof(Sample) * s * nranks, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
+  trace.mark("local_sort+samples(sync)");
   b2s_host_select_splitters(h_samples.data(), h_samples.size(), nranks, h_split.data());
   CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nranks - 1), cudaMemcpyHostToDevice, stream));
 
@@ -337,6 +369,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   std::vector<long long> h_cuts(nranks + 1), h_count((size_t)nranks * nranks);
   CK_CUDA(cudaMemcpyAsync(h_cuts.data(), d_cuts, sizeof(long long) * (nranks + 1), cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
+  trace.mark("cuts(sync)");
   std::vector<long long> send(nranks);
   for (int p = 0; p < nranks; ++p) send[p] = h_cuts[p + 1] - h_cuts[p];
   CK_CUDA(cudaMemcpyAsync(d_count + (size_t)rank * nranks, send.data(), sizeof(long long) * nranks, cudaMemcpyHostToDevice, stream));
@@ -345,6 +378,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   if (barrier) barrier(barrier_ctx);
   CK_CUDA(cudaMemcpyAsync(h_count.data(), d_count, sizeof(long long) * nranks * nranks, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
+  trace.mark("counts(sync)");
   for (long long c : h_count)
     if (c < 0) return B2S_ERR_INVALID_ARG;  // a rank disagreed about the protocol
 
@@ -366,20 +400,25 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     runs.idx[p]  = argsort ? r_idx + recv_off[p] : nullptr;
   }
   const unsigned char* k_bytes = static_cast<const unsigned char*>(keys);
+  trace.mark("alloc_recv");
   if (barrier) barrier(barrier_ctx);
+  prof::begin(prof::K_XCHG, stream);
   CK_NCCL(ncclGroupStart());
-  for (int p = 0; p < nranks; ++p) {
-    if (p == rank) continue;
-    if (send[p] > 0) {
-      CK_NCCL(ncclSend(k_bytes + (size_t)h_cuts[p] * kb, (size_t)send[p] * kb, ncclUint8, p, comm, stream));
-      if (argsort) CK_NCCL(ncclSend(idx + h_cuts[p], (size_t)send[p], ncclInt64, p, comm, stream));
+  // Staggered pairing: in step i every rank sends to (rank + i) and receives from (rank - i), so
+  // no rank is the target of everybody at once.
+  for (int i = 1; i < nranks; ++i) {
+    const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
+    if (send[to] > 0) {
+      CK_NCCL(ncclSend(k_bytes + (size_t)h_cuts[to] * kb, (size_t)send[to] * kb, ncclUint8, to, comm, stream));
+      if (argsort) CK_NCCL(ncclSend(idx + h_cuts[to], (size_t)send[to], ncclInt64, to, comm, stream));
     }
-    if (runs.len[p] > 0) {
-      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[p] * kb, (size_t)runs.len[p] * kb, ncclUint8, p, comm, stream));
-      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[p], (size_t)runs.len[p], ncclInt64, p, comm, stream));
+    if (runs.len[from] > 0) {
+      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[from] * kb, (size_t)runs.len[from] * kb, ncclUint8, from, comm, stream));
+      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[from], (size_t)runs.len[from], ncclInt64, from, comm, stream));
     }
   }
   CK_NCCL(ncclGroupEnd());
+  prof::end(prof::K_XCHG, stream);
   if (barrier) barrier(barrier_ctx);
   if (send[rank] > 0) {  // my own slice stays on this GPU
     CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[rank] * kb, k_bytes + (size_t)h_cuts[rank] * kb,
@@ -389,6 +428,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
                               cudaMemcpyDeviceToDevice, stream));
   }
 
+  trace.mark("enqueue_exchange");
   // ---- 5. stable k-way merge in rank order ----
   void* result = mem.get((size_t)total * (argsort ? 8 : kb));
   if (result == nullptr) return B2S_ERR_WORKSPACE;
@@ -400,8 +440,10 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     int rc = merge_runs(kb, xf, runs, total, argsort != 0, result, static_cast<long long*>(d_tcuts), stream);
     if (rc != B2S_OK) return rc;
   }
+  trace.mark("enqueue_merge");
   // temporaries are handed back only once the stream is done with them
   CK_CUDA(cudaStreamSynchronize(stream));
+  trace.mark("exchange+merge(sync)");
   mem.disown(result);
   *out_ptr = result;
   *out_len = (size_t)total;

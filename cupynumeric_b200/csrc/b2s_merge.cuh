@@ -43,18 +43,33 @@ __device__ __forceinline__ long long lower_bound_okey(const void* base, long lon
 
 // cuts[b * nruns + i] = number of elements of run i among the first b * MERGE_TILE elements of
 // the stable merge; b = 0 .. ntiles.
+//
+// Two launches: the first handles every `stride`-th boundary (coarse == nullptr) and searches
+// the whole runs; the second handles all boundaries and searches only between the two coarse
+// cuts that enclose each one, where both the index range and the key range are narrow.
 template <int KB>
 __global__ void __launch_bounds__(256)
-merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf, long long* __restrict__ cuts)
+merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf, long long* __restrict__ cuts,
+                       long long stride, int fine)
 {
-  const int lane          = threadIdx.x & 31;
-  const long long b       = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (b > ntiles) return;
-  const int nruns         = runs.nruns;
-  const bool mine         = lane < nruns;
-  const long long n_i     = mine ? runs.len[lane] : 0;
-  const void* base        = mine ? runs.keys[lane] : nullptr;
-  long long r             = b * MERGE_TILE;
+  const int lane      = threadIdx.x & 31;
+  const long long w   = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int nruns     = runs.nruns;
+  long long b;
+  if (!fine) {
+    // coarse boundaries: 0, stride, 2*stride, ..., and ntiles itself
+    const long long ncoarse = (ntiles + stride - 1) / stride + 1;
+    if (w >= ncoarse) return;
+    b = w * stride < ntiles ? w * stride : ntiles;
+  } else {
+    if (w > ntiles) return;
+    b = w;
+    if (b % stride == 0 || b == ntiles) return;  // written by the coarse launch
+  }
+  const bool mine     = lane < nruns;
+  const long long n_i = mine ? runs.len[lane] : 0;
+  const void* base    = mine ? runs.keys[lane] : nullptr;
+  long long r         = b * MERGE_TILE;
   if (r > total) r = total;
   long long cut;
   if (r == 0) {
@@ -62,14 +77,21 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
   } else if (r == total) {
     cut = n_i;
   } else {
-    // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit.
+    long long lo = 0, hi = n_i;  // this run's cut lies in [lo, hi]
+    if (fine && mine) {
+      const long long c0 = (b / stride) * stride;
+      const long long c1 = c0 + stride < ntiles ? c0 + stride : ntiles;
+      lo                 = cuts[c0 * nruns + lane];
+      hi                 = cuts[c1 * nruns + lane];
+    }
+    const long long lo0 = lo, hi0 = hi;
     constexpr int BITS = 8 * KB;
-    // Bits above the highest one in which the smallest and the largest key of all runs differ are
-    // common to every key: start the bisection below them.
+    // Bits above the highest one in which the smallest and the largest key of the searched
+    // ranges differ are common to every candidate: start the bisection below them.
     unsigned long long kmin = ~0ull, kmax = 0;
-    if (n_i > 0) {
-      kmin = okey_at<KB>(base, 0, xf);
-      kmax = okey_at<KB>(base, n_i - 1, xf);
+    if (hi > lo) {
+      kmin = okey_at<KB>(base, lo, xf);
+      kmax = okey_at<KB>(base, hi - 1, xf);
     }
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) {
@@ -80,8 +102,9 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
     }
     const unsigned long long diff = kmin ^ kmax;
     const int top = diff ? 63 - __clzll((long long)diff) : -1;  // highest varying bit
+    // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit;
+    // positions outside [lo0, hi0] are known to lie left / right of the cut and count as such.
     unsigned long long x = top >= 63 ? 0ull : (top < 0 ? kmin : (kmin >> (top + 1)) << (top + 1));
-    long long lo = 0, hi = n_i;  // lower_bound of every future candidate lies in [lo, hi]
     for (int bit = top < BITS - 1 ? top : BITS - 1; bit >= 0; --bit) {
       const unsigned long long cand = x | (1ull << bit);
       const long long p = lower_bound_okey<KB>(base, lo, hi, cand, xf);
@@ -95,10 +118,12 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
         hi = p;
       }
     }
-    // lo = #(keys < v) in this run; ties (== v) are handed out in run order
+    // lo = #(keys < v) in this run (clamped to the searched range); ties (== v) are handed out
+    // in run order
     const long long lower = lo;
-    long long upper       = n_i;
-    if (x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1))) upper = lower_bound_okey<KB>(base, lo, n_i, x + 1, xf);
+    long long upper       = hi0;
+    if (x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1))) upper = lower_bound_okey<KB>(base, lo, hi0, x + 1, xf);
+    (void)lo0;
     long long less_total = lower;
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) less_total += __shfl_xor_sync(0xFFFFFFFFu, less_total, s);
@@ -115,6 +140,8 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
   }
   if (mine) cuts[b * nruns + lane] = cut;
 }
+
+constexpr long long MERGE_COARSE_STRIDE = 64;
 
 template <int KB, bool ARGS>
 struct MergeSmem {

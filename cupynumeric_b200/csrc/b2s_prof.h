@@ -15,6 +15,7 @@ enum Kind : int {
   K_UNIT,         // segments of one element
   K_DIST,         // sample / splitter / cut kernels of the distributed sort
   K_MERGE,        // k-way merge
+  K_XCHG,         // the grouped NCCL send/recv exchange (not a kernel of this library)
   K_COUNT
 };
 

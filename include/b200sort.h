@@ -183,7 +183,8 @@ typedef enum {
   B2S_K_UNIT    = 5, /* segments of one element */
   B2S_K_DIST    = 6, /* sampling, splitter search and cut kernels of the distributed sort */
   B2S_K_MERGE   = 7, /* k-way merge */
-  B2S_K_COUNT   = 8
+  B2S_K_XCHG    = 8, /* NCCL key/index exchange of the distributed sort (timed, not counted as a launch) */
+  B2S_K_COUNT   = 9
 } b2s_kernel_kind_t;
 
 /* Switches per-launch CUDA-event timing on or off and forgets earlier records.  Process-wide,
