@@ -337,7 +337,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
   Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nranks));
   long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nranks + 1)));
-  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * nranks));
+  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nranks + 1)));
   if (!d_samples || !d_split || !d_cuts || !d_count) return B2S_ERR_WORKSPACE;
   {
     prof::Scope ps(prof::K_DIST, stream);
@@ -366,55 +366,66 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     });
   }
   CK_CUDA(cudaGetLastError());
-  std::vector<long long> h_cuts(nranks + 1), h_count((size_t)nranks * nranks);
-  CK_CUDA(cudaMemcpyAsync(h_cuts.data(), d_cuts, sizeof(long long) * (nranks + 1), cudaMemcpyDeviceToHost, stream));
+  std::vector<long long> h_cuts(nranks + 1), h_allcuts((size_t)nranks * (nranks + 1));
+  // every rank learns every rank's cut positions: counts and the alignment of each slice
+  if (barrier) barrier(barrier_ctx);
+  CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * (nranks + 1), ncclUint8, comm, stream));
+  if (barrier) barrier(barrier_ctx);
+  CK_CUDA(cudaMemcpyAsync(h_allcuts.data(), d_count, sizeof(long long) * nranks * (nranks + 1),
+                          cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
-  trace.mark("cuts(sync)");
+  trace.mark("cuts+counts(sync)");
+  for (int p = 0; p <= nranks; ++p) h_cuts[p] = h_allcuts[(size_t)rank * (nranks + 1) + p];
+  for (int src = 0; src < nranks; ++src)
+    for (int p = 0; p < nranks; ++p)
+      if (h_allcuts[(size_t)src * (nranks + 1) + p] > h_allcuts[(size_t)src * (nranks + 1) + p + 1])
+        return B2S_ERR_INVALID_ARG;  // a rank disagreed about the protocol
   std::vector<long long> send(nranks);
   for (int p = 0; p < nranks; ++p) send[p] = h_cuts[p + 1] - h_cuts[p];
-  CK_CUDA(cudaMemcpyAsync(d_count + (size_t)rank * nranks, send.data(), sizeof(long long) * nranks, cudaMemcpyHostToDevice, stream));
-  if (barrier) barrier(barrier_ctx);
-  CK_NCCL(ncclAllGather(d_count + (size_t)rank * nranks, d_count, sizeof(long long) * nranks, ncclUint8, comm, stream));
-  if (barrier) barrier(barrier_ctx);
-  CK_CUDA(cudaMemcpyAsync(h_count.data(), d_count, sizeof(long long) * nranks * nranks, cudaMemcpyDeviceToHost, stream));
-  CK_CUDA(cudaStreamSynchronize(stream));
-  trace.mark("counts(sync)");
-  for (long long c : h_count)
-    if (c < 0) return B2S_ERR_INVALID_ARG;  // a rank disagreed about the protocol
 
   // ---- 4. exchange: my slice [cuts[p], cuts[p+1]) goes to rank p; runs arrive in rank order ----
+  // A slice starts wherever its splitter cut the sorted data, usually not on a 16-byte boundary,
+  // and NCCL's copies are much slower from unaligned addresses.  So each transfer starts at the
+  // slice's start rounded down to XFER_ALIGN elements; the receiver, who knows the sender's cut
+  // positions, skips those leading elements.  Runs land on aligned offsets of the receive buffer.
+  constexpr long long XFER_ALIGN = 32;
   MergeRuns runs{};
-  runs.nruns        = nranks;
-  long long total   = 0;
-  std::vector<long long> recv_off(nranks);
+  runs.nruns      = nranks;
+  long long total = 0, slots = 0;
+  std::vector<long long> recv_off(nranks), lead(nranks);
   for (int p = 0; p < nranks; ++p) {
-    recv_off[p] = total;
-    runs.len[p] = h_count[(size_t)p * nranks + rank];
+    const long long start = h_allcuts[(size_t)p * (nranks + 1) + rank];
+    const long long end   = h_allcuts[(size_t)p * (nranks + 1) + rank + 1];
+    runs.len[p]           = end - start;
+    lead[p]               = p == rank ? 0 : start % XFER_ALIGN;
+    recv_off[p]           = slots;
+    slots += (lead[p] + runs.len[p] + XFER_ALIGN - 1) / XFER_ALIGN * XFER_ALIGN;
     total += runs.len[p];
   }
-  unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)total * kb));
-  int64_t* r_idx        = argsort ? static_cast<int64_t*>(mem.get((size_t)total * 8)) : nullptr;
+  unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)slots * kb));
+  int64_t* r_idx        = argsort ? static_cast<int64_t*>(mem.get((size_t)slots * 8)) : nullptr;
   if (r_keys == nullptr || (argsort && r_idx == nullptr)) return B2S_ERR_WORKSPACE;
   for (int p = 0; p < nranks; ++p) {
-    runs.keys[p] = r_keys + (size_t)recv_off[p] * kb;
-    runs.idx[p]  = argsort ? r_idx + recv_off[p] : nullptr;
+    runs.keys[p] = r_keys + (size_t)(recv_off[p] + lead[p]) * kb;
+    runs.idx[p]  = argsort ? r_idx + recv_off[p] + lead[p] : nullptr;
   }
   const unsigned char* k_bytes = static_cast<const unsigned char*>(keys);
   trace.mark("alloc_recv");
   if (barrier) barrier(barrier_ctx);
   prof::begin(prof::K_XCHG, stream);
   CK_NCCL(ncclGroupStart());
-  // Staggered pairing: in step i every rank sends to (rank + i) and receives from (rank - i), so
-  // no rank is the target of everybody at once.
   for (int i = 1; i < nranks; ++i) {
     const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
     if (send[to] > 0) {
-      CK_NCCL(ncclSend(k_bytes + (size_t)h_cuts[to] * kb, (size_t)send[to] * kb, ncclUint8, to, comm, stream));
-      if (argsort) CK_NCCL(ncclSend(idx + h_cuts[to], (size_t)send[to], ncclInt64, to, comm, stream));
+      const long long a0 = h_cuts[to] - h_cuts[to] % XFER_ALIGN;
+      const size_t cnt   = (size_t)(h_cuts[to + 1] - a0);
+      CK_NCCL(ncclSend(k_bytes + (size_t)a0 * kb, cnt * kb, ncclUint8, to, comm, stream));
+      if (argsort) CK_NCCL(ncclSend(idx + a0, cnt, ncclInt64, to, comm, stream));
     }
     if (runs.len[from] > 0) {
-      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[from] * kb, (size_t)runs.len[from] * kb, ncclUint8, from, comm, stream));
-      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[from], (size_t)runs.len[from], ncclInt64, from, comm, stream));
+      const size_t cnt = (size_t)(lead[from] + runs.len[from]);
+      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[from] * kb, cnt * kb, ncclUint8, from, comm, stream));
+      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[from], cnt, ncclInt64, from, comm, stream));
     }
   }
   CK_NCCL(ncclGroupEnd());
@@ -450,7 +461,8 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   if (out_global_offset) {
     long long before = 0;  // elements that end up on lower ranks
     for (int d = 0; d < rank; ++d)
-      for (int src = 0; src < nranks; ++src) before += h_count[(size_t)src * nranks + d];
+      for (int src = 0; src < nranks; ++src)
+        before += h_allcuts[(size_t)src * (nranks + 1) + d + 1] - h_allcuts[(size_t)src * (nranks + 1) + d];
     *out_global_offset = before;
   }
   return B2S_OK;
