@@ -143,18 +143,26 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
 
 constexpr long long MERGE_COARSE_STRIDE = 64;
 
+// Shared-memory index of logical position i in the merge buffers.  A thread works on
+// MERGE_VT consecutive positions, so unpadded accesses of a warp would fall on two banks; one
+// spare slot per eight spreads them over all banks.
+__device__ __host__ __forceinline__ constexpr int mpad(int i) { return i + (i >> 3); }
+constexpr int MERGE_PADDED = MERGE_TILE + MERGE_TILE / 8 + 8;
+
 template <int KB, bool ARGS>
 struct MergeSmem {
   static constexpr size_t OFF_RAW  = 0;
   static constexpr size_t OFF_IDX_RAW = OFF_RAW + (size_t)MERGE_TILE * KB;
   static constexpr size_t OFF_IDX  = (OFF_IDX_RAW + 15) / 16 * 16;
-  static constexpr size_t OFF_OK0  = OFF_IDX + (ARGS ? (size_t)MERGE_TILE * 8 : 0);
-  static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_TILE * 8;
-  static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_TILE * 8;
-  static constexpr size_t OFF_SL1  = OFF_SL0 + (size_t)MERGE_TILE * 2;
-  static constexpr size_t OFF_BND  = OFF_SL1 + (size_t)MERGE_TILE * 2;
+  static constexpr size_t OFF_OK0  = OFF_IDX;  // payloads are staged in a merge buffer once the merge is done
+  static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_PADDED * 8;
+  static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_PADDED * 8;
+  static constexpr size_t OFF_SL1  = OFF_SL0 + (size_t)MERGE_PADDED * 2;
+  static constexpr size_t OFF_BND  = (OFF_SL1 + (size_t)MERGE_PADDED * 2 + 15) / 16 * 16;
   static constexpr size_t OFF_SRC  = (OFF_BND + (MERGE_MAX_RUNS + 1) * 4 + 15) / 16 * 16;  // 8-byte entries
-  static constexpr size_t BYTES    = OFF_SRC + MERGE_MAX_RUNS * 8;
+  static constexpr size_t OFF_KP   = OFF_SRC + MERGE_MAX_RUNS * 8;   // run key pointers
+  static constexpr size_t OFF_IP   = OFF_KP + MERGE_MAX_RUNS * 8;    // run payload pointers
+  static constexpr size_t BYTES    = OFF_IP + MERGE_MAX_RUNS * 8;
 };
 
 // One CTA per output tile.  ARGS: emit the int64 payload (argsort); else emit the keys.
@@ -167,22 +175,29 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   using S = MergeSmem<KB, ARGS>;
   extern __shared__ __align__(16) unsigned char smem[];
   K* raw                    = reinterpret_cast<K*>(smem + S::OFF_RAW);
-  int64_t* pay              = reinterpret_cast<int64_t*>(smem + S::OFF_IDX);
   unsigned long long* ok[2] = {reinterpret_cast<unsigned long long*>(smem + S::OFF_OK0),
                                reinterpret_cast<unsigned long long*>(smem + S::OFF_OK1)};
   unsigned short* sl[2]     = {reinterpret_cast<unsigned short*>(smem + S::OFF_SL0),
                                reinterpret_cast<unsigned short*>(smem + S::OFF_SL1)};
-  int* bnd                  = reinterpret_cast<int*>(smem + S::OFF_BND);       // piece starts in the tile
-  long long* src0           = reinterpret_cast<long long*>(smem + S::OFF_SRC); // piece starts in the runs
+  int* bnd                  = reinterpret_cast<int*>(smem + S::OFF_BND);        // piece starts in the tile
+  long long* src0           = reinterpret_cast<long long*>(smem + S::OFF_SRC);  // piece starts in the runs
+  const K** kptr            = reinterpret_cast<const K**>(smem + S::OFF_KP);
+  const int64_t** iptr      = reinterpret_cast<const int64_t**>(smem + S::OFF_IP);
 
-  const int tid         = threadIdx.x;
-  const long long b     = blockIdx.x;
-  const int nruns       = runs.nruns;
-  const long long base  = b * MERGE_TILE;
-  const int count       = (int)((total - base) < MERGE_TILE ? (total - base) : MERGE_TILE);
+  const int tid        = threadIdx.x;
+  const long long b    = blockIdx.x;
+  const int nruns      = runs.nruns;
+  const long long base = b * MERGE_TILE;
+  const int count      = (int)((total - base) < MERGE_TILE ? (total - base) : MERGE_TILE);
   int p2 = 1;
   while (p2 < nruns) p2 <<= 1;  // tree width
 
+  // run descriptors go to shared memory: indexing kernel parameters with a run-time index would
+  // make the compiler spill the whole parameter block to local memory
+  if (tid < MERGE_MAX_RUNS) {
+    kptr[tid] = tid < nruns ? static_cast<const K*>(runs.keys[tid]) : nullptr;
+    iptr[tid] = tid < nruns ? runs.idx[tid] : nullptr;
+  }
   if (tid == 0) {
     int off = 0;
     for (int i = 0; i < nruns; ++i) {
@@ -195,16 +210,16 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   }
   __syncthreads();
 
-  // load the pieces, in run order
-  for (int q = tid; q < count; q += MERGE_THREADS) {
-    int i = 0;
-    while (i + 1 < nruns && bnd[i + 1] <= q) ++i;
-    const long long s = src0[i] + (q - bnd[i]);
-    const K k         = static_cast<const K*>(runs.keys[i])[s];
-    raw[q]            = k;
-    if (ARGS) pay[q] = runs.idx[i][s];
-    ok[0][q] = (unsigned long long)to_ordered_rt<KB>(k, xf);
-    sl[0][q] = (unsigned short)q;
+  // load the pieces, run after run (coalesced inside a run)
+  for (int i = 0; i < nruns; ++i) {
+    const int q0 = bnd[i], q1 = bnd[i + 1];
+    const K* kp  = kptr[i] + src0[i];
+    for (int q = q0 + tid; q < q1; q += MERGE_THREADS) {
+      const K k = kp[q - q0];
+      raw[q]    = k;
+      ok[0][mpad(q)] = (unsigned long long)to_ordered_rt<KB>(k, xf);
+      sl[0][mpad(q)] = (unsigned short)q;
+    }
   }
   __syncthreads();
 
@@ -227,22 +242,27 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
       int lo = max(0, diag - nb), hi = min(diag, na);
       while (lo < hi) {
         const int m = (lo + hi) >> 1;
-        if (ik[s0 + m] <= ik[mid + diag - 1 - m]) lo = m + 1; else hi = m;
+        if (ik[mpad(s0 + m)] <= ik[mpad(mid + diag - 1 - m)]) lo = m + 1; else hi = m;
       }
-      int ia = lo, ib = diag - lo;
-      unsigned long long ka = ia < na ? ik[s0 + ia] : 0, kb = ib < nb ? ik[mid + ib] : 0;
-      for (; q < end; ++q) {
-        const bool take_a = (ib >= nb) || (ia < na && ka <= kb);
-        if (take_a) {
-          okd[q] = ka;
-          sld[q] = is[s0 + ia];
-          ++ia;
-          ka = ia < na ? ik[s0 + ia] : 0;
-        } else {
-          okd[q] = kb;
-          sld[q] = is[mid + ib];
-          ++ib;
-          kb = ib < nb ? ik[mid + ib] : 0;
+      int ia = s0 + lo, ib = mid + diag - lo;  // absolute read positions in the two runs
+      constexpr unsigned long long INF = ~0ull;
+      unsigned long long ka = ia < mid ? ik[mpad(ia)] : INF, kb = ib < s1 ? ik[mpad(ib)] : INF;
+#pragma unroll
+      for (int j = 0; j < MERGE_VT; ++j) {
+        if (q < end) {
+          // an exhausted run reads as +inf; on equal keys the lower run wins unless it is exhausted
+          const bool take_a = ib >= s1 || (ia < mid && ka <= kb);
+          const int from    = take_a ? ia : ib;
+          okd[mpad(q)]      = take_a ? ka : kb;
+          sld[mpad(q)]      = is[mpad(from)];
+          ia += take_a ? 1 : 0;
+          ib += take_a ? 0 : 1;
+          const int nxt              = take_a ? ia : ib;
+          const bool live            = take_a ? (ia < mid) : (ib < s1);
+          const unsigned long long v = live ? ik[mpad(nxt)] : INF;
+          ka = take_a ? v : ka;
+          kb = take_a ? kb : v;
+          ++q;
         }
       }
     }
@@ -252,11 +272,19 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
 
   const unsigned short* fs = sl[cur];
   if (ARGS) {
+    // the merge buffer that is no longer read becomes the payload staging area
+    int64_t* pay = reinterpret_cast<int64_t*>(ok[cur ^ 1]);
+    for (int i = 0; i < nruns; ++i) {
+      const int q0 = bnd[i], q1 = bnd[i + 1];
+      const int64_t* ip = iptr[i] + src0[i];
+      for (int q = q0 + tid; q < q1; q += MERGE_THREADS) pay[q] = ip[q - q0];
+    }
+    __syncthreads();
     int64_t* o = static_cast<int64_t*>(out) + base;
-    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[fs[q]];
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[fs[mpad(q)]];
   } else {
     K* o = static_cast<K*>(out) + base;
-    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[fs[q]];
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[fs[mpad(q)]];
   }
 }
 
