@@ -42,10 +42,13 @@ __host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered(typename
   } else {
     // exponent mask: all exponent bits set = inf/NaN
     constexpr K EXP = (KB == 2) ? (K)0x7C00u : (KB == 4) ? (K)0x7F800000u : (K)0x7FF0000000000000ull;
-    const K mag     = (K)(raw & (K)~SB);
-    if (mag > EXP) { return (K)~(K)0; }           // NaN
-    if (mag == 0) { return SB; }                  // +0.0 and -0.0
-    return (raw & SB) ? (K)~raw : (K)(raw | SB);
+    // straight-line selects: branches here would diverge inside the per-key loops
+    const K mag  = (K)(raw & (K)~SB);
+    const K mask = (raw & SB) ? (K)~(K)0 : SB;   // negative: flip everything; positive: set the sign
+    K o          = (K)(raw ^ mask);
+    o            = mag > EXP ? (K)~(K)0 : o;     // NaN
+    o            = mag == 0 ? SB : o;            // +0.0 and -0.0
+    return o;
   }
 }
 

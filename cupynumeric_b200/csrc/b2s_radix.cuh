@@ -362,15 +362,43 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   }
   __syncthreads();
 
+  // ---- publish this tile's digit counts, then do local work before looking back ----
+  // The permutation inside shared memory needs nothing from other tiles, so it runs between the
+  // publication of the counts and the walk over the predecessors: by then most of them have
+  // published too and the walk rarely has to poll.
+  unsigned int* mine = lookback + (size_t)tile * RADIX + (tid < RADIX ? tid : 0);
+  if (tid < RADIX) {
+    dig_excl[tid] = my_excl_tile;
+    st_relaxed(mine, (tile == 0 ? LB_FLAG_INCL : LB_FLAG_AGG) | my_count);
+  }
+  __syncthreads();
+
+  // ---- permute the tile inside shared memory: position = digit start + earlier rows + rank ----
+  unsigned int pos[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    const unsigned int d = rd[i] >> 16;
+    pos[i]               = dig_excl[d] + my_hist[(i / IPC) * RADIX + d] + (rd[i] & 0xFFFFu);
+    stage_keys[pos[i]]   = key[i];
+  }
+  if (PAIRS) {
+    int64_t val[ITEMS];
+    if (load_idx) {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) val[i] = stage_vals[stripe0 + 32 * i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < ITEMS; ++i) val[i] = index_offset + (int64_t)(tile_base + stripe0 + 32 * i);
+    }
+    __syncthreads();  // every thread holds its indices before any slot is overwritten
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) stage_vals[pos[i]] = val[i];
+  }
+
   // ---- chained prefix over tiles (decoupled look-back), one thread per digit ----
   if (tid < RADIX) {
-    dig_excl[tid]      = my_excl_tile;
-    unsigned int* mine = lookback + (size_t)tile * RADIX + tid;
-    unsigned int excl  = 0;
-    if (tile == 0) {
-      st_relaxed(mine, LB_FLAG_INCL | my_count);
-    } else {
-      st_relaxed(mine, LB_FLAG_AGG | my_count);
+    unsigned int excl = 0;
+    if (tile != 0) {
       // Walk back over the predecessors, LB_WINDOW of them per round trip: the loads of one
       // window are independent, so a run of tiles that have only published their counts costs
       // one memory latency per window instead of one per tile.
@@ -378,9 +406,6 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
       unsigned int spins = 0;
       bool gave_up       = false;
       bool done          = false;
-#ifdef B2S_EXP_NO_LOOKBACK
-      done = true;
-#endif
       while (!done) {
         unsigned int v[LB_WINDOW];
 #pragma unroll
@@ -406,6 +431,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
             gave_up = true;
             break;
           }
+          if (spins > 4) __nanosleep(64);  // leave the issue slots to the other CTAs of the SM
         }
       }
       if (gave_up) raise_timeout(ctrl);
@@ -413,29 +439,6 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
     }
     // global index of a staged element = base_ml[digit] + its position in the staged tile
     base_ml[tid] = ctrl->hist[pass][tid] + excl - my_excl_tile;
-  }
-  __syncthreads();
-
-  // ---- permute the tile inside shared memory: position = digit start + earlier rows + rank ----
-  unsigned int pos[ITEMS];
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const unsigned int d = rd[i] >> 16;
-    pos[i]               = dig_excl[d] + my_hist[(i / IPC) * RADIX + d] + (rd[i] & 0xFFFFu);
-    stage_keys[pos[i]]   = key[i];
-  }
-  if (PAIRS) {
-    int64_t val[ITEMS];
-    if (load_idx) {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) val[i] = stage_vals[stripe0 + 32 * i];
-    } else {
-#pragma unroll
-      for (int i = 0; i < ITEMS; ++i) val[i] = index_offset + (int64_t)(tile_base + stripe0 + 32 * i);
-    }
-    __syncthreads();  // every thread holds its indices before any slot is overwritten
-#pragma unroll
-    for (int i = 0; i < ITEMS; ++i) stage_vals[pos[i]] = val[i];
   }
   __syncthreads();
 
