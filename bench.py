@@ -30,7 +30,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used when MEASURE
 
 # DRAM bytes (read + write) of one onesweep launch per key, from the ncu capture summarised in
 # profiles/ (scaled to a full launch by the number of keys); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_KEY = {"c1": None, "c2": None}
+NCU_TRAFFIC_BYTES_PER_KEY = {"c1": 7.45, "c2": 22.76}  # c2: a middle pass (reads and writes key + index)
 
 
 def measured_hbm_peak():
@@ -91,7 +91,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-i", str(self.index), "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:

@@ -50,6 +50,27 @@ inline cudaError_t radix_any(int kb, int xf, const void* in, void* out, int64_t*
   }
 }
 
+inline size_t radix_seg_ws(int kb, size_t seg_len, size_t nseg, bool pairs)
+{
+  switch (kb) {
+    case 1: return radix_seg_layout<1>(seg_len, nseg, pairs).total;
+    case 2: return radix_seg_layout<2>(seg_len, nseg, pairs).total;
+    case 4: return radix_seg_layout<4>(seg_len, nseg, pairs).total;
+    default: return radix_seg_layout<8>(seg_len, nseg, pairs).total;
+  }
+}
+
+inline cudaError_t radix_seg_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int seg_len,
+                                 unsigned int nseg, int64_t off, unsigned char* ws, cudaStream_t s)
+{
+  switch (kb) {
+    case 1: return launch_radix_seg<1>(xf, in, out, idx, seg_len, nseg, off, ws, s);
+    case 2: return launch_radix_seg<2>(xf, in, out, idx, seg_len, nseg, off, ws, s);
+    case 4: return launch_radix_seg<4>(xf, in, out, idx, seg_len, nseg, off, ws, s);
+    default: return launch_radix_seg<8>(xf, in, out, idx, seg_len, nseg, off, ws, s);
+  }
+}
+
 inline cudaError_t seg_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int L,
                            unsigned long long nseg, int64_t off, Ctrl* ctrl, cudaStream_t s)
 {
@@ -73,9 +94,9 @@ __global__ void unit_segment_kernel(const unsigned char* in, unsigned char* out,
     for (size_t i = gthread; i < volume; i += gstride) idx[i] = index_offset;
 }
 
-// Segments longer than the on-chip kernel takes are sorted one after the other by the 1-D path
-// while there are few of them.
-constexpr size_t MAX_LOOPED_SEGMENTS = 4096;
+// Several segments longer than the on-chip kernel takes go through the segmented onesweep; its
+// element offsets are 32-bit, so one call takes fewer than 2^32 elements.
+constexpr size_t MAX_SEG_VOLUME = (size_t)1 << 32;
 
 }  // namespace b2s
 
@@ -108,7 +129,12 @@ int b2s_workspace_bytes(int dtype, size_t volume, size_t segment, int argsort, s
   size_t need = align_up(sizeof(Ctrl), 256);
   if (volume > 0 && segment > SEG_CAP) {
     if (segment >= MAX_N_1D) return B2S_ERR_UNSUPPORTED;
-    need = radix_ws(di.kb, segment, argsort != 0);
+    if (volume == segment) {
+      need = radix_ws(di.kb, segment, argsort != 0);
+    } else {
+      if (volume >= MAX_SEG_VOLUME) return B2S_ERR_UNSUPPORTED;
+      need = radix_seg_ws(di.kb, segment, volume / segment, argsort != 0);
+    }
   }
   *bytes = need;
   return B2S_OK;
@@ -150,16 +176,14 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
     return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
   }
 
-  if (nseg > MAX_LOOPED_SEGMENTS) return B2S_ERR_UNSUPPORTED;
-  for (size_t s = 0; s < nseg; ++s) {
-    const unsigned char* in = static_cast<const unsigned char*>(keys_in) + s * segment * di.kb;
-    unsigned char* out = keys_out ? static_cast<unsigned char*>(keys_out) + s * segment * di.kb : nullptr;
-    int64_t* idx       = idx_out ? idx_out + s * segment : nullptr;
-    e = radix_any(di.kb, di.xf, in, out, idx, (unsigned int)segment, index_offset, static_cast<unsigned char*>(ws),
-                  stream);
-    if (e != cudaSuccess) return B2S_ERR_CUDA;
+  if (nseg == 1) {
+    e = radix_any(di.kb, di.xf, keys_in, keys_out, idx_out, (unsigned int)segment, index_offset,
+                  static_cast<unsigned char*>(ws), stream);
+  } else {
+    e = radix_seg_any(di.kb, di.xf, keys_in, keys_out, idx_out, (unsigned int)segment, (unsigned int)nseg,
+                      index_offset, static_cast<unsigned char*>(ws), stream);
   }
-  return B2S_OK;
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 
 int b2s_check_status(void* ws, void* cuda_stream)

@@ -93,7 +93,7 @@ inline Radix1dLayout radix_1d_layout(size_t n, bool pairs)
 }
 
 template <int KB, int XF, bool PAIRS>
-inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned int tiles, unsigned int n,
+inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned int tiles, SegGeom geo,
                                  int64_t index_offset, cudaStream_t stream)
 {
   using C   = SweepCfg<KB, PAIRS>;
@@ -103,7 +103,7 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
   if (e != cudaSuccess) return e;
   for (int pass = 0; pass < KB; ++pass) {
     prof::Scope ps(prof::K_SWEEP, stream);
-    kern<<<tiles, C::THREADS, S::BYTES, stream>>>(ctrl, lookback + (size_t)pass * tiles * RADIX, pass, n,
+    kern<<<tiles, C::THREADS, S::BYTES, stream>>>(ctrl, lookback + (size_t)pass * tiles * RADIX, pass, geo,
                                                   index_offset);
   }
   return cudaGetLastError();
@@ -145,8 +145,9 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
     prof::Scope ps(prof::K_SCAN, stream);
     scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
   }
-  e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, n, index_offset, stream)
-            : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, n, index_offset, stream);
+  const SegGeom geo{n, lay.tiles, 1u, KB, nullptr};
+  e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, geo, index_offset, stream)
+            : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, geo, index_offset, stream);
   if (e != cudaSuccess) return e;
   unsigned int fgrid = (n + 256 * 16 - 1) / (256 * 16);
   if (fgrid > (unsigned int)sms * 8) fgrid = sms * 8;
@@ -156,6 +157,90 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   }
   return cudaGetLastError();
 }
+
+// ---- segments too long for the on-chip kernel: onesweep passes whose tiles stay inside segments ----
+struct RadixSegLayout {
+  size_t off_lookback, off_seghist, off_keys[2], off_idx[2], total;
+  unsigned int tiles_per_seg, tiles;
+};
+
+template <int KB>
+inline RadixSegLayout radix_seg_layout(size_t seg_len, size_t nseg, bool pairs)
+{
+  RadixSegLayout l{};
+  const unsigned int tile = pairs ? SweepCfg<KB, true>::TILE : SweepCfg<KB, false>::TILE;
+  l.tiles_per_seg         = (unsigned int)((seg_len + tile - 1) / tile);
+  l.tiles                 = (unsigned int)(l.tiles_per_seg * nseg);
+  const size_t volume     = seg_len * nseg;
+  size_t off              = align_up(sizeof(Ctrl), 256);
+  l.off_lookback          = off;
+  off += align_up((size_t)KB * l.tiles * RADIX * sizeof(unsigned int), 256);
+  l.off_seghist = off;
+  off += align_up(nseg * KB * RADIX * sizeof(unsigned int), 256);
+  for (int i = 0; i < 2; ++i) {
+    l.off_keys[i] = off;
+    off += align_up(volume * KB, 256);
+  }
+  for (int i = 0; i < 2; ++i) {
+    l.off_idx[i] = off;
+    if (pairs) off += align_up(volume * 8, 256);
+  }
+  l.total = off;
+  return l;
+}
+
+template <int KB, int XF>
+inline cudaError_t radix_seg_xf(const void* in, void* out, int64_t* idx_out, unsigned int seg_len, unsigned int nseg,
+                                int64_t index_offset, unsigned char* ws, cudaStream_t stream)
+{
+  using K          = typename KeyOf<KB>::type;
+  const bool pairs = idx_out != nullptr;
+  const auto lay   = radix_seg_layout<KB>(seg_len, nseg, pairs);
+  Ctrl* ctrl       = reinterpret_cast<Ctrl*>(ws);
+  unsigned int* lb = reinterpret_cast<unsigned int*>(ws + lay.off_lookback);
+  unsigned int* sh = reinterpret_cast<unsigned int*>(ws + lay.off_seghist);
+  cudaError_t e    = cudaMemsetAsync(ws, 0, lay.off_keys[0], stream);  // control block, look-back table, histograms
+  if (e != cudaSuccess) return e;
+  const unsigned int chunks = (seg_len + SEG_HIST_CHUNK - 1) / SEG_HIST_CHUNK;
+  {
+    prof::Scope ps(prof::K_HIST, stream);
+    seg_hist_kernel<KB, XF><<<nseg * chunks, 256, 0, stream>>>(static_cast<const K*>(in), seg_len, chunks, sh);
+  }
+  {
+    prof::Scope ps(prof::K_SCAN, stream);
+    seg_scan_kernel<<<nseg * KB, RADIX, 0, stream>>>(sh);
+  }
+  RouteArgs ra{};
+  ra.keys_in     = in;
+  ra.keys_out    = out;
+  ra.idx_out     = idx_out;
+  ra.tmp_keys[0] = ws + lay.off_keys[0];
+  ra.tmp_keys[1] = ws + lay.off_keys[1];
+  ra.tmp_idx[0]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[0]);
+  ra.tmp_idx[1]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[1]);
+  ra.n           = seg_len * nseg;
+  ra.npass       = KB;
+  ra.key_bytes   = KB;
+  {
+    // the global histogram stays empty here, so every pass is routed as active
+    prof::Scope ps(prof::K_SCAN, stream);
+    scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
+  }
+  const SegGeom geo{seg_len, lay.tiles_per_seg, nseg, KB, sh};
+  e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, geo, index_offset, stream)
+            : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, geo, index_offset, stream);
+  if (e != cudaSuccess) return e;
+  {
+    prof::Scope ps(prof::K_FIXUP, stream);
+    fixup_kernel<<<148 * 4, 256, 0, stream>>>(ctrl, seg_len * nseg, index_offset);
+  }
+  return cudaGetLastError();
+}
+
+// Segments of more than SEG_CAP elements (each below 2^30, fewer than 2^32 elements in all).
+template <int KB>
+cudaError_t launch_radix_seg(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
+                             unsigned int nseg, int64_t index_offset, unsigned char* ws, cudaStream_t stream);
 
 // 1-D stable sort of n < 2^30 keys. `ws` must hold radix_1d_layout<KB>(n, idx_out != null).total bytes.
 template <int KB>
@@ -211,6 +296,17 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
     if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream); \
     if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
       return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream); \
+    return cudaErrorInvalidValue;                                                                         \
+  }                                                                                                       \
+  template <>                                                                                             \
+  cudaError_t launch_radix_seg<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len, \
+                                   unsigned int nseg, int64_t index_offset, unsigned char* ws,           \
+                                   cudaStream_t stream)                                                   \
+  {                                                                                                       \
+    if (xf == XF_UNSIGNED) return radix_seg_xf<KB, XF_UNSIGNED>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
+    if (xf == XF_SIGNED) return radix_seg_xf<KB, XF_SIGNED>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
+    if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
+      return radix_seg_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
     return cudaErrorInvalidValue;                                                                         \
   }                                                                                                       \
   template <>                                                                                             \

@@ -158,6 +158,57 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
 }
 
 // ---------------------------------------------------------------------------------------------
+// Per-segment variants of kernels 1 and 2 for segments too long for the on-chip sort: one CTA
+// counts one chunk of one segment; a second kernel turns each 256-bin histogram into bases.
+// ---------------------------------------------------------------------------------------------
+constexpr unsigned int SEG_HIST_CHUNK = 8192;
+
+template <int KB, int XF>
+__global__ void __launch_bounds__(256)
+seg_hist_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int seg_len, unsigned int chunks_per_seg,
+                unsigned int* __restrict__ seg_hist)
+{
+  __shared__ unsigned int sh[KB][RADIX];
+  for (int i = threadIdx.x; i < KB * RADIX; i += 256) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  const unsigned int seg = blockIdx.x / chunks_per_seg, chunk = blockIdx.x - seg * chunks_per_seg;
+  const unsigned int lo  = chunk * SEG_HIST_CHUNK;
+  const unsigned int hi  = min(seg_len, lo + SEG_HIST_CHUNK);
+  const auto* base       = keys + (size_t)seg * seg_len;
+  for (unsigned int i = lo + threadIdx.x; i < hi; i += 256) {
+    const auto k = to_ordered<KB, XF>(base[i]);
+#pragma unroll
+    for (int p = 0; p < KB; ++p) atomicAdd(&sh[p][(unsigned int)(k >> (8 * p)) & 0xFFu], 1u);
+  }
+  __syncthreads();
+  unsigned int* out = seg_hist + (size_t)seg * KB * RADIX;
+  for (int i = threadIdx.x; i < KB * RADIX; i += 256) {
+    const unsigned int c = (&sh[0][0])[i];
+    if (c) atomicAdd(out + i, c);
+  }
+}
+
+// One CTA of 256 threads per (segment, pass): counts -> exclusive bases, in place.
+static __global__ void __launch_bounds__(RADIX) seg_scan_kernel(unsigned int* __restrict__ seg_hist)
+{
+  __shared__ unsigned int warp_tot[RADIX / 32];
+  unsigned int* h      = seg_hist + (size_t)blockIdx.x * RADIX;
+  const int d          = threadIdx.x, lane = d & 31, w = d >> 5;
+  const unsigned int c = h[d];
+  unsigned int incl    = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_tot[w] = incl;
+  __syncthreads();
+  unsigned int base = 0;
+  for (int i = 0; i < w; ++i) base += warp_tot[i];
+  h[d] = base + incl - c;
+}
+
+// ---------------------------------------------------------------------------------------------
 // Kernel 4: the rare leftovers described by FixDesc.
 // ---------------------------------------------------------------------------------------------
 static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, unsigned int n, int64_t index_offset)
@@ -202,7 +253,7 @@ constexpr unsigned int LB_FLAG_INCL = 2u << 30;  // inclusive prefix published
 constexpr unsigned int LB_VALUE     = (1u << 30) - 1;
 constexpr unsigned int MAX_N_1D     = 1u << 30;  // counts must fit 30 bits
 #ifndef B2S_CFG_LB_WINDOW
-#define B2S_CFG_LB_WINDOW 1
+#define B2S_CFG_LB_WINDOW 4
 #endif
 constexpr int LB_WINDOW             = B2S_CFG_LB_WINDOW;  // predecessors inspected per round trip
 
@@ -222,9 +273,21 @@ struct SweepSmem {
   static constexpr size_t BYTES     = OFF_MISC + 8;
 };
 
+// Segment geometry of a launch.  A 1-D sort is one segment of n keys.  Tiles never straddle
+// segments: tile t belongs to segment t / tiles_per_seg, and each segment has its own chain of
+// look-back entries (its first tile publishes an inclusive prefix at once) and its own digit
+// bases (seg_bases; null for the 1-D case, whose bases live in the control block).
+struct SegGeom {
+  unsigned int seg_len;
+  unsigned int tiles_per_seg;
+  unsigned int nseg;
+  int npass;
+  const unsigned int* seg_bases;  // [nseg][npass][RADIX] exclusive digit bases, or null
+};
+
 template <int KB, int XF, bool PAIRS, int THREADS, int ITEMS, int CHAINS, int MIN_CTAS>
 __global__ void __launch_bounds__(THREADS, MIN_CTAS)
-onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsigned int n, int64_t index_offset)
+onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGeom geo, int64_t index_offset)
 {
   using K = typename KeyOf<KB>::type;
   using S = SweepSmem<KB, PAIRS, THREADS, ITEMS, CHAINS>;
@@ -252,9 +315,6 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   const int shift   = pass * RADIX_BITS;
   const DigitSel ds = make_digit_sel<KB, XF>(pass);
 
-  const K* src_keys      = static_cast<const K*>(pd.src_keys);
-  const int64_t* src_idx = pd.src_idx;
-
   if (tid == 0) {
     misc[0] = atomicAdd(&ctrl->tile_counter[pass], 1u);
     mbar_init(bar, 1);
@@ -262,14 +322,19 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   }
   for (int i = tid; i < ROWS * RADIX; i += THREADS) hist[i] = 0;
   __syncthreads();
-  const unsigned int tile      = misc[0];
-  const unsigned int tile_base = tile * TILE;
-  if (tile_base >= n) return;  // more CTAs than tiles
-  const unsigned int valid = min((unsigned int)TILE, n - tile_base);
+  const unsigned int tile = misc[0];
+  const unsigned int seg  = tile / geo.tiles_per_seg;
+  if (seg >= geo.nseg) return;  // more CTAs than tiles
+  const unsigned int t_in      = tile - seg * geo.tiles_per_seg;  // tile number inside its segment
+  const unsigned int tile_base = t_in * TILE;                     // first element, segment-relative
+  const size_t seg_off         = (size_t)seg * geo.seg_len;
+  const unsigned int valid     = min((unsigned int)TILE, geo.seg_len - tile_base);
+  const K* src_keys            = static_cast<const K*>(pd.src_keys) + seg_off;
+  const int64_t* src_idx       = pd.src_idx ? pd.src_idx + seg_off : nullptr;
   const bool full          = valid == TILE;
   const bool load_idx      = PAIRS && src_idx != nullptr;
-  const bool use_bulk      = full && ((reinterpret_cast<uintptr_t>(src_keys) & 15u) == 0) &&
-                        (!load_idx || (reinterpret_cast<uintptr_t>(src_idx) & 15u) == 0);
+  const bool use_bulk      = full && ((reinterpret_cast<uintptr_t>(src_keys + tile_base) & 15u) == 0) &&
+                        (!load_idx || (reinterpret_cast<uintptr_t>(src_idx + tile_base) & 15u) == 0);
 
   // ---- load the tile; keys end up in registers in warp-striped order ----
   K key[ITEMS];
@@ -369,7 +434,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   unsigned int* mine = lookback + (size_t)tile * RADIX + (tid < RADIX ? tid : 0);
   if (tid < RADIX) {
     dig_excl[tid] = my_excl_tile;
-    st_relaxed(mine, (tile == 0 ? LB_FLAG_INCL : LB_FLAG_AGG) | my_count);
+    st_relaxed(mine, (t_in == 0 ? LB_FLAG_INCL : LB_FLAG_AGG) | my_count);
   }
   __syncthreads();
 
@@ -398,8 +463,9 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
   // ---- chained prefix over tiles (decoupled look-back), one thread per digit ----
   if (tid < RADIX) {
     unsigned int excl = 0;
-    if (tile != 0) {
-      // Walk back over the predecessors, LB_WINDOW of them per round trip: the loads of one
+    if (t_in != 0) {
+      // Walk back over the predecessors (the segment's first tile always holds an inclusive
+      // prefix, so the walk never leaves the segment), LB_WINDOW of them per round trip: the loads of one
       // window are independent, so a run of tiles that have only published their counts costs
       // one memory latency per window instead of one per tile.
       int t              = (int)tile - 1;
@@ -438,13 +504,15 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, unsig
       st_relaxed(mine, LB_FLAG_INCL | ((excl + my_count) & LB_VALUE));
     }
     // global index of a staged element = base_ml[digit] + its position in the staged tile
-    base_ml[tid] = ctrl->hist[pass][tid] + excl - my_excl_tile;
+    const unsigned int* bases =
+      geo.seg_bases ? geo.seg_bases + ((size_t)seg * geo.npass + pass) * RADIX : ctrl->hist[pass];
+    base_ml[tid] = bases[tid] + excl - my_excl_tile;
   }
   __syncthreads();
 
   // ---- coalesced scatter: consecutive threads store consecutive elements of a digit's run ----
-  K* dst_keys       = static_cast<K*>(__builtin_assume_aligned(pd.dst_keys, sizeof(K)));
-  int64_t* dst_idx  = pd.dst_idx;
+  K* dst_keys       = pd.dst_keys ? static_cast<K*>(pd.dst_keys) + seg_off : nullptr;
+  int64_t* dst_idx  = pd.dst_idx ? pd.dst_idx + seg_off : nullptr;
   const bool wr_key = dst_keys != nullptr;
   if (full) {
 #pragma unroll

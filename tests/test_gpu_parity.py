@@ -70,7 +70,7 @@ def test_constant_and_presorted_inputs_skip_passes(cuda_device, dtype):
 
 # ---- segmented (axis sorts) --------------------------------------------------------------------
 SEGMENTS = [(7, 1), (5, 2), (1000, 3), (64, 12), (33, 128), (20, 129), (9, 1000), (5, 1024), (3, 1025),
-            (4, 4096), (3, 4097), (2, 8192), (3, 8193), (2, 20000)]
+            (4, 4096), (3, 4097), (2, 8192), (3, 8193), (2, 20000), (37, 8200), (6, 50001)]
 
 
 @pytest.mark.parametrize("dtype", ALL_DTYPES)
