@@ -137,14 +137,20 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
     {
       prof::Scope ps(prof::K_DIST, stream);
       const long long ncoarse = (ntiles + MERGE_COARSE_STRIDE - 1) / MERGE_COARSE_STRIDE + 1;
-      merge_partition_kernel<KB><<<(unsigned int)((ncoarse + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts,
-                                                                                   MERGE_COARSE_STRIDE, 0);
+      int gw = 1;
+      while (gw < runs.nruns) gw <<= 1;
+      const long long per_cta = 8 * (32 / gw);  // boundaries per CTA of 8 warps
+      merge_partition_kernel<KB><<<(unsigned int)((ncoarse + per_cta - 1) / per_cta), 256, 0, stream>>>(
+        runs, total, ntiles, xf, d_tcuts, MERGE_COARSE_STRIDE, 0);
     }
     {
       prof::Scope ps(prof::K_DIST, stream);
       const long long warps = ntiles + 1;
-      merge_partition_kernel<KB><<<(unsigned int)((warps + 7) / 8), 256, 0, stream>>>(runs, total, ntiles, xf, d_tcuts,
-                                                                                 MERGE_COARSE_STRIDE, 1);
+      int gw = 1;
+      while (gw < runs.nruns) gw <<= 1;
+      const long long per_cta = 8 * (32 / gw);
+      merge_partition_kernel<KB><<<(unsigned int)((warps + per_cta - 1) / per_cta), 256, 0, stream>>>(
+        runs, total, ntiles, xf, d_tcuts, MERGE_COARSE_STRIDE, 1);
     }
     prof::Scope ps(prof::K_MERGE, stream);
     if (args) {

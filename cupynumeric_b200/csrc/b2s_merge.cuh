@@ -52,65 +52,68 @@ __global__ void __launch_bounds__(256)
 merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf, long long* __restrict__ cuts,
                        long long stride, int fine)
 {
+  // A warp is split into groups of gw lanes (gw = run count rounded up to a power of two); each
+  // group finds one boundary, one lane per run.  All groups run the same number of loop trips so
+  // that the warp stays converged for the shuffles.
+  const int nruns = runs.nruns;
+  int gw = 1;
+  while (gw < nruns) gw <<= 1;
+  const int groups    = 32 / gw;
   const int lane      = threadIdx.x & 31;
-  const long long w   = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int nruns     = runs.nruns;
-  long long b;
+  const int sub       = lane / gw, run = lane % gw;
+  const long long w   = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * groups + sub;
+  long long b         = 0;
+  bool live           = true;
   if (!fine) {
     // coarse boundaries: 0, stride, 2*stride, ..., and ntiles itself
     const long long ncoarse = (ntiles + stride - 1) / stride + 1;
-    if (w >= ncoarse) return;
-    b = w * stride < ntiles ? w * stride : ntiles;
+    live = w < ncoarse;
+    b    = w * stride < ntiles ? w * stride : ntiles;
   } else {
-    if (w > ntiles) return;
-    b = w;
-    if (b % stride == 0 || b == ntiles) return;  // written by the coarse launch
+    live = w <= ntiles;
+    b    = w;
+    if (live && (b % stride == 0 || b == ntiles)) live = false;  // written by the coarse launch
   }
-  const bool mine     = lane < nruns;
-  const long long n_i = mine ? runs.len[lane] : 0;
-  const void* base    = mine ? runs.keys[lane] : nullptr;
+  const bool mine     = live && run < nruns;
+  const long long n_i = mine ? runs.len[run] : 0;
+  const void* base    = mine ? runs.keys[run] : nullptr;
   long long r         = b * MERGE_TILE;
   if (r > total) r = total;
-  long long cut;
-  if (r == 0) {
-    cut = 0;
-  } else if (r == total) {
-    cut = n_i;
-  } else {
-    long long lo = 0, hi = n_i;  // this run's cut lies in [lo, hi]
-    if (fine && mine) {
-      const long long c0 = (b / stride) * stride;
-      const long long c1 = c0 + stride < ntiles ? c0 + stride : ntiles;
-      lo                 = cuts[c0 * nruns + lane];
-      hi                 = cuts[c1 * nruns + lane];
-    }
-    const long long lo0 = lo, hi0 = hi;
-    constexpr int BITS = 8 * KB;
-    // Bits above the highest one in which the smallest and the largest key of the searched
-    // ranges differ are common to every candidate: start the bisection below them.
-    unsigned long long kmin = ~0ull, kmax = 0;
-    if (hi > lo) {
-      kmin = okey_at<KB>(base, lo, xf);
-      kmax = okey_at<KB>(base, hi - 1, xf);
-    }
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) {
-      const unsigned long long a = __shfl_xor_sync(0xFFFFFFFFu, kmin, s);
-      const unsigned long long c = __shfl_xor_sync(0xFFFFFFFFu, kmax, s);
-      kmin = a < kmin ? a : kmin;
-      kmax = c > kmax ? c : kmax;
-    }
-    const unsigned long long diff = kmin ^ kmax;
-    const int top = diff ? 63 - __clzll((long long)diff) : -1;  // highest varying bit
-    // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit;
-    // positions outside [lo0, hi0] are known to lie left / right of the cut and count as such.
-    unsigned long long x = top >= 63 ? 0ull : (top < 0 ? kmin : (kmin >> (top + 1)) << (top + 1));
-    for (int bit = top < BITS - 1 ? top : BITS - 1; bit >= 0; --bit) {
-      const unsigned long long cand = x | (1ull << bit);
-      const long long p = lower_bound_okey<KB>(base, lo, hi, cand, xf);
-      long long less = p;
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1) less += __shfl_xor_sync(0xFFFFFFFFu, less, s);
+  const bool search   = live && r > 0 && r < total;
+
+  long long lo = 0, hi = search ? n_i : 0;  // this run's cut lies in [lo, hi]
+  if (search && fine && mine) {
+    const long long c0 = (b / stride) * stride;
+    const long long c1 = c0 + stride < ntiles ? c0 + stride : ntiles;
+    lo                 = cuts[c0 * nruns + run];
+    hi                 = cuts[c1 * nruns + run];
+  }
+  const long long hi0 = hi;
+  constexpr int BITS  = 8 * KB;
+  // Bits above the highest one in which the smallest and the largest key of the searched ranges
+  // differ are common to every candidate: the bisection starts below them.
+  unsigned long long kmin = ~0ull, kmax = 0;
+  if (hi > lo) {
+    kmin = okey_at<KB>(base, lo, xf);
+    kmax = okey_at<KB>(base, hi - 1, xf);
+  }
+  for (int s = gw >> 1; s > 0; s >>= 1) {
+    const unsigned long long a = __shfl_xor_sync(0xFFFFFFFFu, kmin, s);
+    const unsigned long long c = __shfl_xor_sync(0xFFFFFFFFu, kmax, s);
+    kmin = a < kmin ? a : kmin;
+    kmax = c > kmax ? c : kmax;
+  }
+  const unsigned long long diff = kmax >= kmin ? (kmin ^ kmax) : 0ull;
+  const int top = diff ? 63 - __clzll((long long)diff) : -1;  // highest varying bit
+  // v = key of the r-th element of the merge = max{x : #(keys < x) <= r}, built bit by bit.
+  unsigned long long x = top >= 63 ? 0ull : (top < 0 ? kmin : (kmin >> (top + 1)) << (top + 1));
+  for (int bit = BITS - 1; bit >= 0; --bit) {
+    const bool step               = search && bit <= top;
+    const unsigned long long cand = x | (1ull << bit);
+    const long long p = step ? lower_bound_okey<KB>(base, lo, hi, cand, xf) : 0;
+    long long less    = p;
+    for (int s = gw >> 1; s > 0; s >>= 1) less += __shfl_xor_sync(0xFFFFFFFFu, less, s);
+    if (step) {
       if (less <= r) {
         x  = cand;
         lo = p;
@@ -118,27 +121,26 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
         hi = p;
       }
     }
-    // lo = #(keys < v) in this run (clamped to the searched range); ties (== v) are handed out
-    // in run order
-    const long long lower = lo;
-    long long upper       = hi0;
-    if (x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1))) upper = lower_bound_okey<KB>(base, lo, hi0, x + 1, xf);
-    (void)lo0;
-    long long less_total = lower;
-#pragma unroll
-    for (int s = 16; s > 0; s >>= 1) less_total += __shfl_xor_sync(0xFFFFFFFFu, less_total, s);
-    const long long equal = upper - lower;
-    long long incl        = equal;  // inclusive prefix of `equal` over lanes
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {
-      const long long t = __shfl_up_sync(0xFFFFFFFFu, incl, s);
-      if (lane >= s) incl += t;
-    }
-    long long take = (r - less_total) - (incl - equal);  // ties left for this run
-    take           = take < 0 ? 0 : (take > equal ? equal : take);
-    cut            = lower + take;
   }
-  if (mine) cuts[b * nruns + lane] = cut;
+  // lo = #(keys < v) in this run (clamped to the searched range); ties (== v) go out in run order
+  const long long lower = lo;
+  long long upper       = hi0;
+  if (search && x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1)))
+    upper = lower_bound_okey<KB>(base, lo, hi0, x + 1, xf);
+  long long less_total = lower;
+  for (int s = gw >> 1; s > 0; s >>= 1) less_total += __shfl_xor_sync(0xFFFFFFFFu, less_total, s);
+  const long long equal = upper - lower;
+  long long incl        = equal;  // inclusive prefix of `equal` over the group's lanes
+  for (int s = 1; s < gw; s <<= 1) {
+    const long long t = __shfl_up_sync(0xFFFFFFFFu, incl, s, gw);
+    if (run >= s) incl += t;
+  }
+  long long take = (r - less_total) - (incl - equal);  // ties left for this run
+  take           = take < 0 ? 0 : (take > equal ? equal : take);
+  long long cut  = lower + take;
+  if (r == 0) cut = 0;
+  if (r == total) cut = mine ? runs.len[run] : 0;
+  if (mine) cuts[b * nruns + run] = cut;
 }
 
 constexpr long long MERGE_COARSE_STRIDE = 64;
