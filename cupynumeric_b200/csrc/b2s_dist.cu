@@ -153,17 +153,19 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
         runs, total, ntiles, xf, d_tcuts, MERGE_COARSE_STRIDE, 1);
     }
     prof::Scope ps(prof::K_MERGE, stream);
-    if (args) {
-      auto kern = merge_tiles_kernel<KB, true>;
-      cudaError_t ee = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MergeSmem<KB, true>::BYTES);
+    auto launch = [&](auto kern, size_t bytes) {
+      cudaError_t ee = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
       if (ee != cudaSuccess) return ee;
-      kern<<<(unsigned int)ntiles, MERGE_THREADS, MergeSmem<KB, true>::BYTES, stream>>>(runs, total, xf, d_tcuts, out);
-    } else {
-      auto kern = merge_tiles_kernel<KB, false>;
-      cudaError_t ee = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MergeSmem<KB, false>::BYTES);
-      if (ee != cudaSuccess) return ee;
-      kern<<<(unsigned int)ntiles, MERGE_THREADS, MergeSmem<KB, false>::BYTES, stream>>>(runs, total, xf, d_tcuts, out);
-    }
+      kern<<<(unsigned int)ntiles, MERGE_THREADS, bytes, stream>>>(runs, total, xf, d_tcuts, out);
+      return cudaSuccess;
+    };
+    const bool flt = xf == XF_FLOAT;
+    cudaError_t ee;
+    if (args && flt) ee = launch(merge_tiles_kernel<KB, true, true>, MergeSmem<KB, true, true>::BYTES);
+    else if (args) ee = launch(merge_tiles_kernel<KB, true, false>, MergeSmem<KB, true, false>::BYTES);
+    else if (flt) ee = launch(merge_tiles_kernel<KB, false, true>, MergeSmem<KB, false, true>::BYTES);
+    else ee = launch(merge_tiles_kernel<KB, false, false>, MergeSmem<KB, false, false>::BYTES);
+    if (ee != cudaSuccess) return ee;
     return cudaGetLastError();
   });
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;

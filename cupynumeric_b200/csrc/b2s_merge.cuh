@@ -151,30 +151,45 @@ constexpr long long MERGE_COARSE_STRIDE = 64;
 __device__ __host__ __forceinline__ constexpr int mpad(int i) { return i + (i >> 3); }
 constexpr int MERGE_PADDED = MERGE_TILE + MERGE_TILE / 8 + 8;
 
-template <int KB, bool ARGS>
+// FLT: float keys, whose ordered image cannot be mapped back (NaN payloads, signed zeros).
+// Slots (the position a merged element had when it was loaded) are carried only when something
+// has to be fetched through them afterwards: the payload (ARGS) or the raw float key (FLT).
+// Plain integer key merges move nothing but the ordered keys and map them back on the way out.
+template <int KB, bool ARGS, bool FLT>
 struct MergeSmem {
+  static constexpr bool SLOTS = ARGS || FLT;
+  static constexpr bool RAW   = FLT && !ARGS;
   static constexpr size_t OFF_RAW  = 0;
-  static constexpr size_t OFF_IDX_RAW = OFF_RAW + (size_t)MERGE_TILE * KB;
-  static constexpr size_t OFF_IDX  = (OFF_IDX_RAW + 15) / 16 * 16;
-  static constexpr size_t OFF_OK0  = OFF_IDX;  // payloads are staged in a merge buffer once the merge is done
+  static constexpr size_t OFF_OK0  = (RAW ? ((size_t)MERGE_TILE * KB + 15) / 16 * 16 : 0);
   static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_PADDED * 8;
   static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_PADDED * 8;
-  static constexpr size_t OFF_SL1  = OFF_SL0 + (size_t)MERGE_PADDED * 2;
-  static constexpr size_t OFF_BND  = (OFF_SL1 + (size_t)MERGE_PADDED * 2 + 15) / 16 * 16;
+  static constexpr size_t OFF_SL1  = OFF_SL0 + (SLOTS ? (size_t)MERGE_PADDED * 2 : 0);
+  static constexpr size_t OFF_BND  = (OFF_SL1 + (SLOTS ? (size_t)MERGE_PADDED * 2 : 0) + 15) / 16 * 16;
   static constexpr size_t OFF_SRC  = (OFF_BND + (MERGE_MAX_RUNS + 1) * 4 + 15) / 16 * 16;  // 8-byte entries
   static constexpr size_t OFF_KP   = OFF_SRC + MERGE_MAX_RUNS * 8;   // run key pointers
   static constexpr size_t OFF_IP   = OFF_KP + MERGE_MAX_RUNS * 8;    // run payload pointers
   static constexpr size_t BYTES    = OFF_IP + MERGE_MAX_RUNS * 8;
 };
 
+// inverse of to_ordered for the integer orderings
+template <int KB>
+__device__ __forceinline__ typename KeyOf<KB>::type from_ordered_int(unsigned long long o, int xf)
+{
+  using K        = typename KeyOf<KB>::type;
+  constexpr K SB = (K)((K)1 << (8 * KB - 1));
+  return xf == XF_SIGNED ? (K)((K)o ^ SB) : (K)o;
+}
+
 // One CTA per output tile.  ARGS: emit the int64 payload (argsort); else emit the keys.
-template <int KB, bool ARGS>
+template <int KB, bool ARGS, bool FLT>
 __global__ void __launch_bounds__(MERGE_THREADS)
 merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __restrict__ cuts,
                    void* __restrict__ out)
 {
   using K = typename KeyOf<KB>::type;
-  using S = MergeSmem<KB, ARGS>;
+  using S = MergeSmem<KB, ARGS, FLT>;
+  constexpr bool SLOTS = S::SLOTS;
+  constexpr bool RAW   = S::RAW;
   extern __shared__ __align__(16) unsigned char smem[];
   K* raw                    = reinterpret_cast<K*>(smem + S::OFF_RAW);
   unsigned long long* ok[2] = {reinterpret_cast<unsigned long long*>(smem + S::OFF_OK0),
@@ -218,9 +233,9 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     const K* kp  = kptr[i] + src0[i];
     for (int q = q0 + tid; q < q1; q += MERGE_THREADS) {
       const K k = kp[q - q0];
-      raw[q]    = k;
+      if (RAW) raw[q] = k;
       ok[0][mpad(q)] = (unsigned long long)to_ordered_rt<KB>(k, xf);
-      sl[0][mpad(q)] = (unsigned short)q;
+      if (SLOTS) sl[0][mpad(q)] = (unsigned short)q;
     }
   }
   __syncthreads();
@@ -256,7 +271,7 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
           const bool take_a = ib >= s1 || (ia < mid && ka <= kb);
           const int from    = take_a ? ia : ib;
           okd[mpad(q)]      = take_a ? ka : kb;
-          sld[mpad(q)]      = is[mpad(from)];
+          if (SLOTS) sld[mpad(q)] = is[mpad(from)];
           ia += take_a ? 1 : 0;
           ib += take_a ? 0 : 1;
           const int nxt              = take_a ? ia : ib;
@@ -284,9 +299,13 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     __syncthreads();
     int64_t* o = static_cast<int64_t*>(out) + base;
     for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[fs[mpad(q)]];
-  } else {
+  } else if (RAW) {
     K* o = static_cast<K*>(out) + base;
     for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[fs[mpad(q)]];
+  } else {
+    K* o                         = static_cast<K*>(out) + base;
+    const unsigned long long* fk = ok[cur];
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = from_ordered_int<KB>(fk[mpad(q)], xf);
   }
 }
 
