@@ -100,6 +100,12 @@ constexpr size_t MAX_SEG_VOLUME = (size_t)1 << 32;
 
 }  // namespace b2s
 
+namespace b2s {
+int complex_ws_bytes(int dtype, size_t volume, size_t segment, size_t* bytes);
+int complex_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t volume,
+                       size_t segment, int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream);
+}  // namespace b2s
+
 using namespace b2s;
 
 extern "C" {
@@ -124,6 +130,10 @@ int b2s_workspace_bytes(int dtype, size_t volume, size_t segment, int argsort, s
 {
   DtypeInfo di;
   if (bytes == nullptr) return B2S_ERR_INVALID_ARG;
+  if (dtype == B2S_COMPLEX64 || dtype == B2S_COMPLEX128) {
+    if (volume > 0 && (segment == 0 || volume % segment != 0)) return B2S_ERR_INVALID_ARG;
+    return complex_ws_bytes(dtype, volume, segment, bytes);
+  }
   if (!dtype_info(dtype, &di)) return B2S_ERR_UNSUPPORTED;
   if (volume > 0 && (segment == 0 || volume % segment != 0)) return B2S_ERR_INVALID_ARG;
   size_t need = align_up(sizeof(Ctrl), 256);
@@ -146,6 +156,11 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
 {
   (void)stable;  // always stable
   DtypeInfo di;
+  if (dtype == B2S_COMPLEX64 || dtype == B2S_COMPLEX128) {
+    if (ndim_is_1 && volume != segment) return B2S_ERR_INVALID_ARG;
+    return complex_local_sort(dtype, keys_in, keys_out, idx_out, volume, segment, index_offset, ws, ws_bytes,
+                              static_cast<cudaStream_t>(cuda_stream));
+  }
   if (!dtype_info(dtype, &di)) return B2S_ERR_UNSUPPORTED;
   if (volume == 0) return B2S_OK;
   if (keys_in == nullptr || (keys_out == nullptr && idx_out == nullptr)) return B2S_ERR_INVALID_ARG;

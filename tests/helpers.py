@@ -50,6 +50,8 @@ def cabi_local_sort(keys: np.ndarray, segment: int, argsort: bool, index_offset:
 def bits(a: np.ndarray) -> np.ndarray:
     """Bit pattern view for exact comparison of floats (NaN payloads, signed zeros)."""
     a = np.ascontiguousarray(a)
+    if a.dtype.kind == "c":
+        return a.view(np.uint32 if a.dtype.itemsize == 8 else np.uint64)
     return a.view({1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[a.dtype.itemsize])
 
 

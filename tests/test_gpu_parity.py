@@ -113,16 +113,21 @@ def test_reference_golden_vectors_through_api(cuda_device):
 
     sort_g = json.load(open(os.path.join(GOLDEN, "sort_cc.json")))
     arg_g = json.load(open(os.path.join(GOLDEN, "argsort_cc.json")))
-    for dtype in ("int32", "float64"):
+    def arr(values, dtype):
+        if dtype == "complex64":
+            return np.array([complex(r, i) for r, i in values], dtype=np.complex64)
+        return np.array(values, dtype=dtype)
+
+    for dtype in ("int32", "float64", "complex64"):
         for shape, table in zip(sort_g["shapes"], sort_g[dtype]["expect"]):
-            a = np.array(sort_g[dtype]["input"], dtype=dtype).reshape(shape)
+            a = arr(sort_g[dtype]["input"], dtype).reshape(shape)
             for axis, expect in table.items():
                 for kind in ("quicksort", "mergesort", "heapsort", "stable"):
                     got = num.sort(a, axis=int(axis), kind=kind).to_numpy()
-                    assert np.array_equal(got, np.array(expect, dtype=dtype).reshape(shape)), (shape, axis)
+                    assert np.array_equal(got, arr(expect, dtype).reshape(shape)), (shape, axis)
         for group in ("basic", "stable"):
             for shape, table in zip(arg_g["shapes"], arg_g["expect"]):
-                a = np.array(arg_g[group][dtype], dtype=dtype).reshape(shape)
+                a = arr(arg_g[group][dtype], dtype).reshape(shape)
                 for axis, expect in table.items():
                     got = num.argsort(a, axis=int(axis), kind="stable").to_numpy()
                     assert np.array_equal(got, np.array(expect, dtype=np.int64).reshape(shape))
@@ -140,6 +145,20 @@ def test_reference_golden_vectors_through_api(cuda_device):
         for axis in range(-len(shape) + 1, len(shape)):
             assert np.array_equal(num.sort(a, axis=axis).to_numpy(), a)
             assert np.array_equal(num.argsort(a, axis=axis).to_numpy(), np.zeros(shape, dtype=np.int64))
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+def test_complex_lexicographic_order(cuda_device, dtype):
+    """(real, imag) lexicographic, stable; many ties in the real parts."""
+    rng = np.random.default_rng(77)
+    for n, seg in ((1, 1), (1000, 1000), (70_000, 70_000), (64 * 300, 300), (5 * 9000, 9000)):
+        a = (rng.integers(-20, 20, n) + 1j * rng.integers(-20, 20, n)).astype(dtype)
+        want_k, want_i = expected(a, seg, True, index_offset=5, ndim_is_1=seg == n)
+        got_k, got_i = cabi_local_sort(a, seg, True, index_offset=5, ndim_is_1=seg == n, want_keys_too=True)
+        assert np.array_equal(got_i, want_i), (n, seg)
+        assert np.array_equal(got_k, want_k)
+        got_k, _ = cabi_local_sort(a, seg, False, ndim_is_1=seg == n, inplace=True)
+        assert np.array_equal(got_k, want_k)
 
 
 # ---- the reference's Python test shapes (tests/integration/test_sort.py:21-40) -----------------
