@@ -1,0 +1,117 @@
+"""Micro-benchmarks of single kernels through the C ABI, with CUDA-event timing per kernel family.
+
+    python -m cupynumeric_b200.kernel_bench merge --dtype int64 --runs 8 --log2 27 [--payload]
+    python -m cupynumeric_b200.kernel_bench sort  --dtype float32 --log2 28 [--argsort] [--segment L]
+
+`merge` times b2s_kway_merge on `runs` sorted runs holding 2^log2 elements in all; `sort` times
+b2s_local_sort.  Small cases of these commands are what the ncu summaries under profiles/ capture.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._thunk._sort import local_sort_tile
+
+KINDS = ["hist", "scan", "sweep", "fixup", "segsort", "unit", "dist", "merge", "xchg"]
+
+
+def _random(dtype: torch.dtype, n: int) -> torch.Tensor:
+    if dtype.is_floating_point:
+        return torch.randn(n, device="cuda", dtype=dtype)
+    info = torch.iinfo(dtype)
+    return torch.randint(max(info.min, -2**62), min(info.max, 2**62), (n,), device="cuda", dtype=torch.int64).to(dtype)
+
+
+def _report(lib, iters: int) -> str:
+    out = []
+    for k, name in enumerate(KINDS):
+        tot, cnt = ctypes.c_double(), ctypes.c_ulonglong()
+        lib.b2s_profile_read(k, ctypes.byref(tot), ctypes.byref(cnt))
+        if cnt.value:
+            out.append(f"{name} {tot.value / iters:.3f} ms ({cnt.value // iters} launches)")
+    return ", ".join(out)
+
+
+def bench_merge(args) -> None:
+    lib = _lib.lib()
+    dtype = getattr(torch, args.dtype)
+    n_each = (1 << args.log2) // args.runs
+    runs = [torch.sort(_random(dtype, n_each)).values for _ in range(args.runs)]
+    pays = [torch.arange(n_each, device="cuda", dtype=torch.int64) + i * n_each for i in range(args.runs)] if args.payload else None
+    total = n_each * args.runs
+    kp = (ctypes.c_void_p * args.runs)(*[r.data_ptr() for r in runs])
+    pp = (ctypes.c_void_p * args.runs)(*[p.data_ptr() for p in pays]) if pays else None
+    lens = (ctypes.c_size_t * args.runs)(*([n_each] * args.runs))
+    need = ctypes.c_size_t()
+    _lib.check(lib.b2s_kway_merge_workspace_bytes(total, args.runs, ctypes.byref(need)), "workspace")
+    ws = torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda")
+    out = torch.empty(total, dtype=torch.int64 if pays else dtype, device="cuda")
+    code = _lib.DTYPE_CODE[np.dtype(args.dtype)]
+
+    def call():
+        _lib.check(lib.b2s_kway_merge(code, args.runs, kp, pp, lens, out.data_ptr(), ws.data_ptr(), ws.numel(),
+                                      torch.cuda.current_stream().cuda_stream), "b2s_kway_merge")
+
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    lib.b2s_profile_enable(1)
+    for _ in range(args.iters):
+        call()
+    torch.cuda.synchronize()
+    print(f"merge {args.dtype} runs={args.runs} total=2^{args.log2} payload={bool(pays)}: {_report(lib, args.iters)}")
+    lib.b2s_profile_enable(0)
+
+
+def bench_sort(args) -> None:
+    lib = _lib.lib()
+    dtype = getattr(torch, args.dtype)
+    n = 1 << args.log2
+    x = _random(dtype, n)
+    if args.segment:
+        x = x.reshape(-1, args.segment)
+    out = torch.empty(x.shape, dtype=torch.int64 if args.argsort else dtype, device="cuda")
+    for _ in range(args.warmup):
+        local_sort_tile(x, args.argsort, True, out=out)
+    torch.cuda.synchronize()
+    lib.b2s_profile_enable(1)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.iters):
+        local_sort_tile(x, args.argsort, True, out=out)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.iters
+    print(f"sort {args.dtype} n=2^{args.log2} segment={args.segment or n} argsort={args.argsort}: {ms:.3f} ms "
+          f"-> {n / ms / 1e6:.1f} Gkeys/s; {_report(lib, args.iters)}")
+    lib.b2s_profile_enable(0)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    sub = ap.add_subparsers(dest="what", required=True)
+    m = sub.add_parser("merge")
+    m.add_argument("--dtype", default="int64")
+    m.add_argument("--runs", type=int, default=8)
+    m.add_argument("--log2", type=int, default=27)
+    m.add_argument("--payload", action="store_true")
+    s = sub.add_parser("sort")
+    s.add_argument("--dtype", default="float32")
+    s.add_argument("--log2", type=int, default=28)
+    s.add_argument("--argsort", action="store_true")
+    s.add_argument("--segment", type=int, default=0)
+    for p in (m, s):
+        p.add_argument("--iters", type=int, default=5)
+        p.add_argument("--warmup", type=int, default=2)
+    args = ap.parse_args()
+    torch.cuda.set_device(0)
+    (bench_merge if args.what == "merge" else bench_sort)(args)
+
+
+if __name__ == "__main__":
+    main()
