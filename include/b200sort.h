@@ -20,7 +20,7 @@
  *   - the sort is always stable, whatever `stable` says (the reference's radix
  *     path ignores the flag too, src/cupynumeric/sort/sort.cu:63-81); floats sort
  *     as -inf < ... < -0.0 == +0.0 < ... < +inf < NaN with the input's bit
- *     patterns preserved.
+ *     patterns preserved; complex keys sort by (real, imaginary).
  */
 #ifndef B200SORT_H_
 #define B200SORT_H_
