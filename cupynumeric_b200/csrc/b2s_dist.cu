@@ -171,6 +171,24 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 
+// Phases of the exchange/merge pipeline.
+#ifndef B2S_DIST_PHASES
+#define B2S_DIST_PHASES 2
+#endif
+constexpr int DIST_PHASES = B2S_DIST_PHASES;
+
+// One extra stream per device for the exchange, created on first use and kept.
+static cudaStream_t exchange_stream()
+{
+  static cudaStream_t streams[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (streams[dev] == nullptr) {
+    if (cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+  }
+  return streams[dev];
+}
+
 // Host-side phase trace of the distributed sort (B2S_DIST_TRACE=1, rank 0 prints).
 struct PhaseTrace {
   bool on;
@@ -340,12 +358,16 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   }
 
   trace.mark("enqueue_local_sort");
-  // ---- 2. samples: all-gather, order on the host, pick nranks-1 splitters ----
+  // ---- 2. samples: all-gather, order on the host, pick the splitters ----
+  // Each destination's value range is cut once more into PH consecutive sub-ranges ("phases"):
+  // while the runs of phase k are being merged, NCCL already moves the runs of phase k+1.
+  const int nph      = DIST_PHASES;  // the same on every rank by construction
+  const int nb       = nranks * nph;  // buckets: bucket q goes to rank q / nph in phase q % nph
   const int s        = SAMPLES_PER_RANK;
   Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
-  Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nranks));
-  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nranks + 1)));
-  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nranks + 1)));
+  Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nb));
+  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 1)));
+  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 1)));
   if (!d_samples || !d_split || !d_cuts || !d_count) return B2S_ERR_WORKSPACE;
   {
     prof::Scope ps(prof::K_DIST, stream);
@@ -358,111 +380,141 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   if (barrier) barrier(barrier_ctx);
   CK_NCCL(ncclAllGather(d_samples + (size_t)rank * s, d_samples, sizeof(Sample) * s, ncclUint8, comm, stream));
   if (barrier) barrier(barrier_ctx);
-  std::vector<Sample> h_samples((size_t)s * nranks), h_split(nranks);
+  std::vector<Sample> h_samples((size_t)s * nranks), h_split(nb);
   CK_CUDA(cudaMemcpyAsync(h_samples.data(), d_samples, sizeof(Sample) * s * nranks, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
   trace.mark("local_sort+samples(sync)");
-  b2s_host_select_splitters(h_samples.data(), h_samples.size(), nranks, h_split.data());
-  CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nranks - 1), cudaMemcpyHostToDevice, stream));
+  b2s_host_select_splitters(h_samples.data(), h_samples.size(), nb, h_split.data());
+  CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nb - 1), cudaMemcpyHostToDevice, stream));
 
-  // ---- 3. where the splitters cut my data; exchange the counts ----
+  // ---- 3. where the splitters cut my data; every rank learns every rank's cut positions ----
   {
     prof::Scope ps(prof::K_DIST, stream);
     by_width(kb, [&](auto w) {
-      cut_kernel<decltype(w)::value><<<(nranks + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nranks, rank, xf, d_cuts);
+      cut_kernel<decltype(w)::value><<<(nb + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nb, rank, xf, d_cuts);
       return cudaSuccess;
     });
   }
   CK_CUDA(cudaGetLastError());
-  std::vector<long long> h_cuts(nranks + 1), h_allcuts((size_t)nranks * (nranks + 1));
-  // every rank learns every rank's cut positions: counts and the alignment of each slice
+  const size_t row = (size_t)nb + 1;
+  std::vector<long long> h_allcuts((size_t)nranks * row);
   if (barrier) barrier(barrier_ctx);
-  CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * (nranks + 1), ncclUint8, comm, stream));
+  CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * row, ncclUint8, comm, stream));
   if (barrier) barrier(barrier_ctx);
-  CK_CUDA(cudaMemcpyAsync(h_allcuts.data(), d_count, sizeof(long long) * nranks * (nranks + 1),
-                          cudaMemcpyDeviceToHost, stream));
+  CK_CUDA(cudaMemcpyAsync(h_allcuts.data(), d_count, sizeof(long long) * nranks * row, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
   trace.mark("cuts+counts(sync)");
-  for (int p = 0; p <= nranks; ++p) h_cuts[p] = h_allcuts[(size_t)rank * (nranks + 1) + p];
   for (int src = 0; src < nranks; ++src)
-    for (int p = 0; p < nranks; ++p)
-      if (h_allcuts[(size_t)src * (nranks + 1) + p] > h_allcuts[(size_t)src * (nranks + 1) + p + 1])
-        return B2S_ERR_INVALID_ARG;  // a rank disagreed about the protocol
-  std::vector<long long> send(nranks);
-  for (int p = 0; p < nranks; ++p) send[p] = h_cuts[p + 1] - h_cuts[p];
+    for (int q = 0; q < nb; ++q)
+      if (h_allcuts[src * row + q] > h_allcuts[src * row + q + 1]) return B2S_ERR_INVALID_ARG;  // protocol mismatch
+  const long long* my_cuts = &h_allcuts[(size_t)rank * row];
 
-  // ---- 4. exchange: my slice [cuts[p], cuts[p+1]) goes to rank p; runs arrive in rank order ----
-  // A slice starts wherever its splitter cut the sorted data, usually not on a 16-byte boundary,
-  // and NCCL's copies are much slower from unaligned addresses.  So each transfer starts at the
-  // slice's start rounded down to XFER_ALIGN elements; the receiver, who knows the sender's cut
-  // positions, skips those leading elements.  Runs land on aligned offsets of the receive buffer.
+  // ---- 4. exchange and merge, phase by phase ----
+  // My slice [cuts[q], cuts[q+1]) of bucket q goes to rank q / nph.  A slice starts wherever its
+  // splitter cut the sorted data, usually not on a 16-byte boundary, and NCCL's copies are much
+  // slower from unaligned addresses: each transfer starts at the slice's start rounded down to
+  // XFER_ALIGN elements and the receiver, who knows the sender's cut positions, skips the
+  // leading elements.  Runs land on aligned offsets of the receive buffer.
   constexpr long long XFER_ALIGN = 32;
-  MergeRuns runs{};
-  runs.nruns      = nranks;
+  std::vector<MergeRuns> runs(nph);
+  std::vector<std::vector<long long>> recv_off(nph, std::vector<long long>(nranks)), lead(nph, std::vector<long long>(nranks));
+  std::vector<long long> ph_total(nph, 0);
   long long total = 0, slots = 0;
-  std::vector<long long> recv_off(nranks), lead(nranks);
-  for (int p = 0; p < nranks; ++p) {
-    const long long start = h_allcuts[(size_t)p * (nranks + 1) + rank];
-    const long long end   = h_allcuts[(size_t)p * (nranks + 1) + rank + 1];
-    runs.len[p]           = end - start;
-    lead[p]               = p == rank ? 0 : start % XFER_ALIGN;
-    recv_off[p]           = slots;
-    slots += (lead[p] + runs.len[p] + XFER_ALIGN - 1) / XFER_ALIGN * XFER_ALIGN;
-    total += runs.len[p];
+  for (int ph = 0; ph < nph; ++ph) {
+    runs[ph]       = MergeRuns{};
+    runs[ph].nruns = nranks;
+    const int q    = rank * nph + ph;
+    for (int p = 0; p < nranks; ++p) {
+      const long long start = h_allcuts[p * row + q], end = h_allcuts[p * row + q + 1];
+      runs[ph].len[p] = end - start;
+      lead[ph][p]     = p == rank ? 0 : start % XFER_ALIGN;
+      recv_off[ph][p] = slots;
+      slots += (lead[ph][p] + runs[ph].len[p] + XFER_ALIGN - 1) / XFER_ALIGN * XFER_ALIGN;
+      ph_total[ph] += runs[ph].len[p];
+    }
+    total += ph_total[ph];
   }
   unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)slots * kb));
   int64_t* r_idx        = argsort ? static_cast<int64_t*>(mem.get((size_t)slots * 8)) : nullptr;
-  if (r_keys == nullptr || (argsort && r_idx == nullptr)) return B2S_ERR_WORKSPACE;
-  for (int p = 0; p < nranks; ++p) {
-    runs.keys[p] = r_keys + (size_t)(recv_off[p] + lead[p]) * kb;
-    runs.idx[p]  = argsort ? r_idx + recv_off[p] + lead[p] : nullptr;
+  void* result          = mem.get((size_t)total * (argsort ? 8 : kb));
+  if (r_keys == nullptr || (argsort && r_idx == nullptr) || result == nullptr) return B2S_ERR_WORKSPACE;
+  std::vector<void*> tcuts(nph, nullptr);
+  for (int ph = 0; ph < nph; ++ph) {
+    for (int p = 0; p < nranks; ++p) {
+      runs[ph].keys[p] = r_keys + (size_t)(recv_off[ph][p] + lead[ph][p]) * kb;
+      runs[ph].idx[p]  = argsort ? r_idx + recv_off[ph][p] + lead[ph][p] : nullptr;
+    }
+    if (ph_total[ph] > 0) {
+      size_t mws = 0;
+      b2s_kway_merge_workspace_bytes((size_t)ph_total[ph], nranks, &mws);
+      tcuts[ph] = mem.get(mws);
+      if (tcuts[ph] == nullptr) return B2S_ERR_WORKSPACE;
+    }
   }
   const unsigned char* k_bytes = static_cast<const unsigned char*>(keys);
   trace.mark("alloc_recv");
-  if (barrier) barrier(barrier_ctx);
-  prof::begin(prof::K_XCHG, stream);
-  CK_NCCL(ncclGroupStart());
-  for (int i = 1; i < nranks; ++i) {
-    const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
-    if (send[to] > 0) {
-      const long long a0 = h_cuts[to] - h_cuts[to] % XFER_ALIGN;
-      const size_t cnt   = (size_t)(h_cuts[to + 1] - a0);
-      CK_NCCL(ncclSend(k_bytes + (size_t)a0 * kb, cnt * kb, ncclUint8, to, comm, stream));
-      if (argsort) CK_NCCL(ncclSend(idx + a0, cnt, ncclInt64, to, comm, stream));
-    }
-    if (runs.len[from] > 0) {
-      const size_t cnt = (size_t)(lead[from] + runs.len[from]);
-      CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[from] * kb, cnt * kb, ncclUint8, from, comm, stream));
-      if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[from], cnt, ncclInt64, from, comm, stream));
-    }
-  }
-  CK_NCCL(ncclGroupEnd());
-  prof::end(prof::K_XCHG, stream);
-  if (barrier) barrier(barrier_ctx);
-  if (send[rank] > 0) {  // my own slice stays on this GPU
-    CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[rank] * kb, k_bytes + (size_t)h_cuts[rank] * kb,
-                            (size_t)send[rank] * kb, cudaMemcpyDeviceToDevice, stream));
-    if (argsort)
-      CK_CUDA(cudaMemcpyAsync(r_idx + recv_off[rank], idx + h_cuts[rank], (size_t)send[rank] * 8,
-                              cudaMemcpyDeviceToDevice, stream));
-  }
 
+  // The exchange runs on a stream of its own so that it overlaps the merges on the caller's.
+  cudaStream_t xs = exchange_stream();
+  if (xs == nullptr) return B2S_ERR_CUDA;
+  cudaEvent_t ev_ready = nullptr;
+  std::vector<cudaEvent_t> ev_done(nph, nullptr);
+  CK_CUDA(cudaEventCreateWithFlags(&ev_ready, cudaEventDisableTiming));
+  for (auto& e : ev_done) CK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  CK_CUDA(cudaEventRecord(ev_ready, stream));
+  CK_CUDA(cudaStreamWaitEvent(xs, ev_ready, 0));
+  for (int ph = 0; ph < nph; ++ph) {
+    if (barrier) barrier(barrier_ctx);
+    prof::begin(prof::K_XCHG, xs);
+    CK_NCCL(ncclGroupStart());
+    for (int i = 1; i < nranks; ++i) {
+      const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
+      const long long c0 = my_cuts[to * nph + ph], c1 = my_cuts[to * nph + ph + 1];
+      if (c1 > c0) {
+        const long long a0 = c0 - c0 % XFER_ALIGN;
+        const size_t cnt   = (size_t)(c1 - a0);
+        CK_NCCL(ncclSend(k_bytes + (size_t)a0 * kb, cnt * kb, ncclUint8, to, comm, xs));
+        if (argsort) CK_NCCL(ncclSend(idx + a0, cnt, ncclInt64, to, comm, xs));
+      }
+      if (runs[ph].len[from] > 0) {
+        const size_t cnt = (size_t)(lead[ph][from] + runs[ph].len[from]);
+        CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[ph][from] * kb, cnt * kb, ncclUint8, from, comm, xs));
+        if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[ph][from], cnt, ncclInt64, from, comm, xs));
+      }
+    }
+    CK_NCCL(ncclGroupEnd());
+    prof::end(prof::K_XCHG, xs);
+    if (barrier) barrier(barrier_ctx);
+    CK_CUDA(cudaEventRecord(ev_done[ph], xs));
+  }
   trace.mark("enqueue_exchange");
-  // ---- 5. stable k-way merge in rank order ----
-  void* result = mem.get((size_t)total * (argsort ? 8 : kb));
-  if (result == nullptr) return B2S_ERR_WORKSPACE;
-  if (total > 0) {
-    size_t mws = 0;
-    b2s_kway_merge_workspace_bytes((size_t)total, nranks, &mws);
-    void* d_tcuts = mem.get(mws);
-    if (d_tcuts == nullptr) return B2S_ERR_WORKSPACE;
-    int rc = merge_runs(kb, xf, runs, total, argsort != 0, result, static_cast<long long*>(d_tcuts), stream);
-    if (rc != B2S_OK) return rc;
+
+  // ---- 5. per phase: my own slice, then the stable k-way merge in rank order ----
+  long long out_off = 0;
+  for (int ph = 0; ph < nph; ++ph) {
+    const long long c0 = my_cuts[rank * nph + ph], c1 = my_cuts[rank * nph + ph + 1];
+    if (c1 > c0) {  // my own slice stays on this GPU
+      CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[ph][rank] * kb, k_bytes + (size_t)c0 * kb,
+                              (size_t)(c1 - c0) * kb, cudaMemcpyDeviceToDevice, stream));
+      if (argsort)
+        CK_CUDA(cudaMemcpyAsync(r_idx + recv_off[ph][rank], idx + c0, (size_t)(c1 - c0) * 8,
+                                cudaMemcpyDeviceToDevice, stream));
+    }
+    CK_CUDA(cudaStreamWaitEvent(stream, ev_done[ph], 0));
+    if (ph_total[ph] > 0) {
+      void* dst = static_cast<unsigned char*>(result) + (size_t)out_off * (argsort ? 8 : kb);
+      int rc    = merge_runs(kb, xf, runs[ph], ph_total[ph], argsort != 0, dst, static_cast<long long*>(tcuts[ph]), stream);
+      if (rc != B2S_OK) return rc;
+    }
+    out_off += ph_total[ph];
   }
   trace.mark("enqueue_merge");
   // temporaries are handed back only once the stream is done with them
   CK_CUDA(cudaStreamSynchronize(stream));
+  CK_CUDA(cudaStreamSynchronize(xs));
   trace.mark("exchange+merge(sync)");
+  cudaEventDestroy(ev_ready);
+  for (auto& e : ev_done) cudaEventDestroy(e);
   mem.disown(result);
   *out_ptr = result;
   *out_len = (size_t)total;
@@ -470,7 +522,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     long long before = 0;  // elements that end up on lower ranks
     for (int d = 0; d < rank; ++d)
       for (int src = 0; src < nranks; ++src)
-        before += h_allcuts[(size_t)src * (nranks + 1) + d + 1] - h_allcuts[(size_t)src * (nranks + 1) + d];
+        before += h_allcuts[src * row + (size_t)(d + 1) * nph] - h_allcuts[src * row + (size_t)d * nph];
     *out_global_offset = before;
   }
   return B2S_OK;

@@ -248,6 +248,9 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
 // row of 256 digit counters ("virtual warp"), so the CHAINS counter updates of one loop
 // iteration are independent of each other and their shared-memory latencies overlap.
 // ---------------------------------------------------------------------------------------------
+#ifndef B2S_RANK_ATOMIC
+#define B2S_RANK_ATOMIC 0
+#endif
 constexpr unsigned int LB_FLAG_AGG  = 1u << 30;  // tile count published
 constexpr unsigned int LB_FLAG_INCL = 2u << 30;  // inclusive prefix published
 constexpr unsigned int LB_VALUE     = (1u << 30) - 1;
@@ -266,7 +269,9 @@ struct SweepSmem {
   static constexpr size_t VAL_BYTES = PAIRS ? (size_t)TILE * 8 : 0;
   static constexpr size_t OFF_VALS  = KEY_BYTES;
   static constexpr size_t OFF_HIST  = OFF_VALS + VAL_BYTES;
-  static constexpr size_t OFF_EXCL  = OFF_HIST + (size_t)ROWS * RADIX * 4;
+  // B2S_RANK_ATOMIC: one 256-entry table of lane masks per warp, built with shared-memory atomicOr
+  static constexpr size_t OFF_MASK  = OFF_HIST + (size_t)ROWS * RADIX * 4;
+  static constexpr size_t OFF_EXCL  = OFF_MASK + (B2S_RANK_ATOMIC ? (size_t)WARPS * RADIX * 4 : 0);
   static constexpr size_t OFF_BASE  = OFF_EXCL + RADIX * 4;
   static constexpr size_t OFF_BAR   = OFF_BASE + RADIX * 4;
   static constexpr size_t OFF_MISC  = OFF_BAR + 8;
@@ -320,7 +325,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
     mbar_init(bar, 1);
     fence_mbar_init();
   }
-  for (int i = tid; i < ROWS * RADIX; i += THREADS) hist[i] = 0;
+  for (int i = tid; i < (ROWS + (B2S_RANK_ATOMIC ? S::WARPS : 0)) * RADIX; i += THREADS) hist[i] = 0;
   __syncthreads();
   const unsigned int tile = misc[0];
   const unsigned int seg  = tile / geo.tiles_per_seg;
@@ -378,6 +383,27 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
   unsigned int rd[ITEMS];
   unsigned int* my_hist = hist + (warp * CHAINS) * RADIX;
   const unsigned int lt = lanemask_lt();
+#if B2S_RANK_ATOMIC
+  // Peer masks through shared memory: every lane ORs its bit into the mask of its digit, reads
+  // the mask back, and the group clears it for the next element.  Far fewer instructions than
+  // eight ballots, at the price of more shared-memory traffic.
+  static_assert(CHAINS == 1, "the atomic form keeps one chain");
+  unsigned int* my_mask       = hist + ROWS * RADIX + warp * RADIX;
+  const unsigned int lane_bit = 1u << lane;
+#pragma unroll
+  for (int k = 0; k < ITEMS; ++k) {
+    const unsigned int d = digit_fast<KB, XF>(key[k], ds, shift);
+    atomicOr(&my_mask[d], lane_bit);
+    __syncwarp();
+    const unsigned int peers = my_mask[d];
+    const unsigned int old   = my_hist[d];
+    __syncwarp();
+    my_hist[d] = old + __popc(peers);
+    my_mask[d] = 0;
+    __syncwarp();
+    rd[k] = (d << 16) | (old + __popc(peers & lt));
+  }
+#else
 #pragma unroll
   for (int k = 0; k < IPC; ++k) {
     unsigned int d[CHAINS], peers[CHAINS], old[CHAINS];
@@ -396,6 +422,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 #pragma unroll
     for (int c = 0; c < CHAINS; ++c) rd[c * IPC + k] = (d[c] << 16) | (old[c] + __popc(peers[c] & lt));
   }
+#endif
   __syncthreads();
 
   // ---- per-digit tile counts: exclusive scan over counter rows, then over digits ----
