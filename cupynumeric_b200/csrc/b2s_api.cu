@@ -1,5 +1,7 @@
 // extern "C" entry points of the local sort (declared in include/b200sort.h).
 #include "../../include/b200sort.h"
+#include <cstdlib>
+
 #include "b2s_launch.cuh"
 
 namespace b2s {
@@ -104,6 +106,41 @@ namespace b2s {
 int complex_ws_bytes(int dtype, size_t volume, size_t segment, size_t* bytes);
 int complex_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t volume,
                        size_t segment, int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream);
+// ---- 1-D arrays at or above the single-sort limit: sort chunks, then merge them ----
+// The look-back counts of the radix passes are 30-bit, so one radix sort takes fewer than 2^30
+// keys.  Longer 1-D tiles are cut into chunks of half that, each chunk is sorted on its own and
+// the sorted chunks (at most 32) go through the stable k-way merge in chunk order, which keeps
+// the whole sort stable.  B2S_MAX_1D_LOG2 lowers the limit (a testing aid).
+inline size_t single_sort_limit()
+{
+  const char* e = std::getenv("B2S_MAX_1D_LOG2");
+  if (e != nullptr) {
+    const int v = std::atoi(e);
+    if (v >= 10 && v <= 30) return (size_t)1 << v;
+  }
+  return MAX_N_1D;
+}
+
+struct ChunkLayout {
+  size_t chunk, nchunks, inner, off_keys, off_idx, off_cuts, cuts_bytes, total;
+};
+
+inline int chunk_layout(int dtype, int kb, size_t n, bool argsort, ChunkLayout* l)
+{
+  l->chunk   = single_sort_limit() / 2;
+  l->nchunks = (n + l->chunk - 1) / l->chunk;
+  if (l->nchunks > 32) return B2S_ERR_UNSUPPORTED;
+  l->inner = radix_ws(kb, l->chunk, argsort);
+  (void)dtype;
+  size_t off  = align_up(l->inner, 256);
+  l->off_keys = off; off += align_up(n * kb, 256);
+  l->off_idx  = off; if (argsort) off += align_up(n * 8, 256);
+  b2s_kway_merge_workspace_bytes(n, (int)l->nchunks, &l->cuts_bytes);
+  l->off_cuts = off; off += align_up(l->cuts_bytes, 256);
+  l->total = off;
+  return B2S_OK;
+}
+
 }  // namespace b2s
 
 using namespace b2s;
@@ -138,8 +175,14 @@ int b2s_workspace_bytes(int dtype, size_t volume, size_t segment, int argsort, s
   if (volume > 0 && (segment == 0 || volume % segment != 0)) return B2S_ERR_INVALID_ARG;
   size_t need = align_up(sizeof(Ctrl), 256);
   if (volume > 0 && segment > SEG_CAP) {
-    if (segment >= MAX_N_1D) return B2S_ERR_UNSUPPORTED;
-    if (volume == segment) {
+    if (volume == segment && segment >= single_sort_limit()) {
+      ChunkLayout cl{};
+      const int rc = chunk_layout(dtype, di.kb, segment, argsort != 0, &cl);
+      if (rc != B2S_OK) return rc;
+      need = cl.total;
+    } else if (segment >= MAX_N_1D) {
+      return B2S_ERR_UNSUPPORTED;
+    } else if (volume == segment) {
       need = radix_ws(di.kb, segment, argsort != 0);
     } else {
       if (volume >= MAX_SEG_VOLUME) return B2S_ERR_UNSUPPORTED;
@@ -191,7 +234,37 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
     return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
   }
 
-  if (nseg == 1) {
+  if (nseg == 1 && segment >= single_sort_limit()) {
+    ChunkLayout cl{};
+    rc = chunk_layout(dtype, di.kb, segment, idx_out != nullptr, &cl);
+    if (rc != B2S_OK) return rc;
+    unsigned char* base = static_cast<unsigned char*>(ws);
+    unsigned char* sk   = base + cl.off_keys;
+    int64_t* si         = idx_out ? reinterpret_cast<int64_t*>(base + cl.off_idx) : nullptr;
+    const void* run_keys[32];
+    const int64_t* run_idx[32];
+    size_t run_len[32];
+    for (size_t c = 0; c < cl.nchunks; ++c) {
+      const size_t lo = c * cl.chunk, len = (lo + cl.chunk <= segment) ? cl.chunk : segment - lo;
+      e = radix_any(di.kb, di.xf, static_cast<const unsigned char*>(keys_in) + lo * di.kb, sk + lo * di.kb,
+                    si ? si + lo : nullptr, (unsigned int)len, index_offset + (int64_t)lo, base, stream);
+      if (e != cudaSuccess) return B2S_ERR_CUDA;
+      run_keys[c] = sk + lo * di.kb;
+      run_idx[c]  = si ? si + lo : nullptr;
+      run_len[c]  = len;
+    }
+    if (idx_out != nullptr) {
+      rc = b2s_kway_merge(dtype, (int)cl.nchunks, run_keys, run_idx, run_len, idx_out, base + cl.off_cuts, cl.cuts_bytes,
+                          cuda_stream);
+      if (rc != B2S_OK) return rc;
+    }
+    if (keys_out != nullptr) {
+      rc = b2s_kway_merge(dtype, (int)cl.nchunks, run_keys, nullptr, run_len, keys_out, base + cl.off_cuts, cl.cuts_bytes,
+                          cuda_stream);
+      if (rc != B2S_OK) return rc;
+    }
+    return B2S_OK;
+  } else if (nseg == 1) {
     e = radix_any(di.kb, di.xf, keys_in, keys_out, idx_out, (unsigned int)segment, index_offset,
                   static_cast<unsigned char*>(ws), stream);
   } else {

@@ -68,6 +68,33 @@ def test_constant_and_presorted_inputs_skip_passes(cuda_device, dtype):
         assert np.array_equal(got_i, want_i)
 
 
+def test_chunked_path_above_the_single_sort_limit(cuda_device, monkeypatch):
+    """1-D tiles at or above the single-sort limit are sorted in chunks and merged; the limit is
+    lowered here so that a small array takes that path."""
+    monkeypatch.setenv("B2S_MAX_1D_LOG2", "16")
+    rng = np.random.default_rng(31)
+    for dtype, n in ((np.int32, 300_001), (np.float32, 65_536), (np.uint64, 1_000_000), (np.int8, 70_000)):
+        a = random_keys(rng, dtype, n, "small" if dtype == np.uint64 else "full")
+        want_k, want_i = expected(a, n, True, index_offset=9)
+        got_k, got_i = cabi_local_sort(a, n, True, index_offset=9, want_keys_too=True)
+        assert np.array_equal(got_i, want_i), np.dtype(dtype)
+        assert_bit_equal(got_k, want_k)
+        got_k, _ = cabi_local_sort(a, n, False, inplace=True)
+        assert_bit_equal(got_k, want_k)
+
+
+def test_one_dim_tile_beyond_two_to_the_thirty(cuda_device):
+    """2^30 + 12345 uint8 keys in one tile (chunks of 2^29 + merge).  The expected output follows
+    from the histogram alone: value v repeated count[v] times."""
+    n = (1 << 30) + 12345
+    rng = np.random.default_rng(5)
+    a = rng.integers(0, 256, n, dtype=np.uint8)
+    got, _ = cabi_local_sort(a, n, False)
+    counts = np.bincount(a, minlength=256)
+    assert np.array_equal(np.bincount(got, minlength=256), counts)
+    assert bool(np.all(got[1:] >= got[:-1]))
+
+
 # ---- segmented (axis sorts) --------------------------------------------------------------------
 SEGMENTS = [(7, 1), (5, 2), (1000, 3), (64, 12), (33, 128), (20, 129), (9, 1000), (5, 1024), (3, 1025),
             (4, 4096), (3, 4097), (2, 8192), (3, 8193), (2, 20000), (37, 8200), (6, 50001)]
