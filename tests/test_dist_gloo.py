@@ -136,3 +136,52 @@ def test_two_rank_sample_sort_over_gloo(kind, n, argsort):
     if kind in ("zipf", "all_equal", "nearly_sorted") and total >= 5000:
         # (rank, position) tie-breaking keeps the parts balanced even when one key dominates
         assert max(sizes) <= 0.55 * total, sizes
+
+
+def rows_worker(rank: int, world: int, port: int, ret):
+    """N-D arrays are tiled by rows: every rank sorts its own row block with no exchange; sorting
+    along the tiled axis is refused.  The point task is played by the oracle."""
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cupynumeric_b200._thunk import _sort as sort_mod
+        from cupynumeric_b200._thunk.deferred import DeferredArray, create_deferred_thunk
+        from cupynumeric_b200.runtime import runtime
+        from oracle import np_task_sort
+
+        def fake(tile, argsort, stable, index_offset=0, out=None):
+            a = tile.numpy()
+            res = np_task_sort(a, a.shape[-1], argsort, index_offset=index_offset, ndim_is_1=a.ndim == 1)
+            return torch.from_numpy(np.ascontiguousarray(res.reshape(a.shape)))
+
+        sort_mod.local_sort_tile = fake
+        assert runtime.num_procs == world
+        whole = np.random.default_rng(9).integers(-50, 50, (8, 13)).astype(np.int32)
+        block = whole[rank * 4:(rank + 1) * 4]
+        out = create_deferred_thunk(block.shape, np.int64)
+        out.sort(DeferredArray(torch.from_numpy(block.copy()), global_lo=rank * 4), argsort=True, axis=-1, kind="stable")
+        ok = bool(np.array_equal(out.base.numpy(), np.argsort(block, axis=-1, kind="stable")))
+        refused = False
+        try:
+            out.sort(DeferredArray(torch.from_numpy(block.copy()), global_lo=rank * 4), axis=0)
+        except NotImplementedError:
+            refused = True
+        ret.put((rank, ok, refused))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_blocks_sort_locally_and_tiled_axis_is_refused():
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=rows_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    got = sorted(ret.get(timeout=10) for _ in range(2))
+    assert got == [(0, True, True), (1, True, True)]
