@@ -20,19 +20,19 @@ constexpr unsigned int SEG_CAP = 8192;
 #define B2S_CFG_CHAINS 1
 #endif
 #ifndef B2S_CFG_K4_THREADS
-#define B2S_CFG_K4_THREADS 512
+#define B2S_CFG_K4_THREADS 256
 #endif
 #ifndef B2S_CFG_K4_ITEMS
 #define B2S_CFG_K4_ITEMS 20
 #endif
 #ifndef B2S_CFG_K4_MINCTAS
-#define B2S_CFG_K4_MINCTAS 2
+#define B2S_CFG_K4_MINCTAS 4
 #endif
 #ifndef B2S_CFG_K8_THREADS
 #define B2S_CFG_K8_THREADS 256
 #endif
 #ifndef B2S_CFG_K8_ITEMS
-#define B2S_CFG_K8_ITEMS 24
+#define B2S_CFG_K8_ITEMS 28
 #endif
 #ifndef B2S_CFG_K8_MINCTAS
 #define B2S_CFG_K8_MINCTAS 3
