@@ -80,8 +80,11 @@ constexpr int MAX_PASSES = 8;
 struct PassDesc {
   const void* src_keys;
   void* dst_keys;          // nullptr: this pass does not write keys
-  const int64_t* src_idx;  // nullptr: indices are synthesised from the element position
-  int64_t* dst_idx;
+  // Between passes an index travels as its 32-bit position inside the segment; only the last
+  // pass widens it to int64 and adds the caller's offset.
+  const uint32_t* src_idx;  // nullptr: positions are synthesised from the element position
+  uint32_t* dst_idx32;      // intermediate pass
+  int64_t* dst_idx64;       // last pass: the caller's index output
   int active;              // 0: the digit is constant over the whole array, pass is the identity
   int pad_;
 };

@@ -41,7 +41,7 @@ constexpr unsigned int SEG_CAP = 8192;
 #define B2S_CFG_P4_THREADS 256
 #endif
 #ifndef B2S_CFG_P4_ITEMS
-#define B2S_CFG_P4_ITEMS 20
+#define B2S_CFG_P4_ITEMS 32
 #endif
 #ifndef B2S_CFG_P4_MINCTAS
 #define B2S_CFG_P4_MINCTAS 3
@@ -50,10 +50,10 @@ constexpr unsigned int SEG_CAP = 8192;
 #define B2S_CFG_P8_THREADS 256
 #endif
 #ifndef B2S_CFG_P8_ITEMS
-#define B2S_CFG_P8_ITEMS 24
+#define B2S_CFG_P8_ITEMS 20
 #endif
 #ifndef B2S_CFG_P8_MINCTAS
-#define B2S_CFG_P8_MINCTAS 2
+#define B2S_CFG_P8_MINCTAS 3
 #endif
 template <int KB, bool PAIRS> struct SweepCfg {
   static constexpr int THREADS = PAIRS ? (KB == 8 ? B2S_CFG_P8_THREADS : B2S_CFG_P4_THREADS)
@@ -86,7 +86,7 @@ inline Radix1dLayout radix_1d_layout(size_t n, bool pairs)
   }
   for (int i = 0; i < 2; ++i) {
     l.off_idx[i] = off;
-    if (pairs) off += align_up(n * 8, 256);
+    if (pairs) off += align_up(n * 4, 256);
   }
   l.total = off;
   return l;
@@ -136,8 +136,8 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.idx_out     = idx_out;
   ra.tmp_keys[0] = ws + lay.off_keys[0];
   ra.tmp_keys[1] = ws + lay.off_keys[1];
-  ra.tmp_idx[0]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[0]);
-  ra.tmp_idx[1]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[1]);
+  ra.tmp_idx[0]  = reinterpret_cast<uint32_t*>(ws + lay.off_idx[0]);
+  ra.tmp_idx[1]  = reinterpret_cast<uint32_t*>(ws + lay.off_idx[1]);
   ra.n           = n;
   ra.npass       = KB;
   ra.key_bytes   = KB;
@@ -183,7 +183,7 @@ inline RadixSegLayout radix_seg_layout(size_t seg_len, size_t nseg, bool pairs)
   }
   for (int i = 0; i < 2; ++i) {
     l.off_idx[i] = off;
-    if (pairs) off += align_up(volume * 8, 256);
+    if (pairs) off += align_up(volume * 4, 256);
   }
   l.total = off;
   return l;
@@ -216,8 +216,8 @@ inline cudaError_t radix_seg_xf(const void* in, void* out, int64_t* idx_out, uns
   ra.idx_out     = idx_out;
   ra.tmp_keys[0] = ws + lay.off_keys[0];
   ra.tmp_keys[1] = ws + lay.off_keys[1];
-  ra.tmp_idx[0]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[0]);
-  ra.tmp_idx[1]  = reinterpret_cast<int64_t*>(ws + lay.off_idx[1]);
+  ra.tmp_idx[0]  = reinterpret_cast<uint32_t*>(ws + lay.off_idx[0]);
+  ra.tmp_idx[1]  = reinterpret_cast<uint32_t*>(ws + lay.off_idx[1]);
   ra.n           = seg_len * nseg;
   ra.npass       = KB;
   ra.key_bytes   = KB;

@@ -81,7 +81,7 @@ struct RouteArgs {
   void* keys_out;     // may be null (argsort)
   int64_t* idx_out;   // may be null (sort)
   void* tmp_keys[2];
-  int64_t* tmp_idx[2];
+  uint32_t* tmp_idx[2];
   unsigned int n;
   int npass;
   int key_bytes;
@@ -115,7 +115,7 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
   int m = 0;
   for (int p = 0; p < a.npass; ++p) m += active[p];
   const void* cur_keys   = a.keys_in;
-  const int64_t* cur_idx = nullptr;
+  const uint32_t* cur_idx = nullptr;
   FixDesc fix            = {};
   int j                  = 0;
   for (int p = 0; p < a.npass; ++p) {
@@ -126,8 +126,8 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
       pd.src_keys     = cur_keys;
       pd.src_idx      = cur_idx;
       if (last) {
-        pd.dst_keys = a.keys_out;
-        pd.dst_idx  = a.idx_out;
+        pd.dst_keys  = a.keys_out;
+        pd.dst_idx64 = a.idx_out;
         if (a.keys_out != nullptr && a.keys_out == cur_keys) {
           // a single effective pass over an in-place call: go through a temporary
           pd.dst_keys    = a.tmp_keys[0];
@@ -137,10 +137,10 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
         }
       } else {
         pd.dst_keys = a.tmp_keys[j & 1];
-        pd.dst_idx  = a.idx_out ? a.tmp_idx[j & 1] : nullptr;
+        pd.dst_idx32 = a.idx_out ? a.tmp_idx[j & 1] : nullptr;
       }
       cur_keys = pd.dst_keys;
-      cur_idx  = pd.dst_idx;
+      cur_idx  = pd.dst_idx32;
       ++j;
     }
     ctrl->pass[p] = pd;
@@ -266,7 +266,7 @@ struct SweepSmem {
   static constexpr int WARPS = THREADS / 32;
   static constexpr int ROWS  = WARPS * CHAINS;  // counter rows ("virtual warps")
   static constexpr size_t KEY_BYTES = ((size_t)TILE * KB + 127) / 128 * 128;
-  static constexpr size_t VAL_BYTES = PAIRS ? (size_t)TILE * 8 : 0;
+  static constexpr size_t VAL_BYTES = PAIRS ? (size_t)TILE * 4 : 0;  // positions travel as 32 bits
   static constexpr size_t OFF_VALS  = KEY_BYTES;
   static constexpr size_t OFF_HIST  = OFF_VALS + VAL_BYTES;
   // B2S_RANK_ATOMIC: one 256-entry table of lane masks per warp, built with shared-memory atomicOr
@@ -308,7 +308,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 
   extern __shared__ __align__(128) unsigned char smem[];
   K* stage_keys          = reinterpret_cast<K*>(smem);
-  int64_t* stage_vals    = reinterpret_cast<int64_t*>(smem + S::OFF_VALS);
+  uint32_t* stage_vals   = reinterpret_cast<uint32_t*>(smem + S::OFF_VALS);
   unsigned int* hist     = reinterpret_cast<unsigned int*>(smem + S::OFF_HIST);
   unsigned int* dig_excl = reinterpret_cast<unsigned int*>(smem + S::OFF_EXCL);
   unsigned int* base_ml  = reinterpret_cast<unsigned int*>(smem + S::OFF_BASE);
@@ -335,7 +335,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
   const size_t seg_off         = (size_t)seg * geo.seg_len;
   const unsigned int valid     = min((unsigned int)TILE, geo.seg_len - tile_base);
   const K* src_keys            = static_cast<const K*>(pd.src_keys) + seg_off;
-  const int64_t* src_idx       = pd.src_idx ? pd.src_idx + seg_off : nullptr;
+  const uint32_t* src_idx      = pd.src_idx ? pd.src_idx + seg_off : nullptr;
   const bool full          = valid == TILE;
   const bool load_idx      = PAIRS && src_idx != nullptr;
   const bool use_bulk      = full && ((reinterpret_cast<uintptr_t>(src_keys + tile_base) & 15u) == 0) &&
@@ -347,10 +347,10 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
   if (use_bulk) {
     int arrived = 1;
     if (tid == 0) {
-      const uint32_t bytes = (uint32_t)(TILE * KB) + (load_idx ? (uint32_t)(TILE * 8) : 0u);
+      const uint32_t bytes = (uint32_t)(TILE * KB) + (load_idx ? (uint32_t)(TILE * 4) : 0u);
       mbar_expect_tx(bar, bytes);
       bulk_load(stage_keys, src_keys + tile_base, TILE * KB, bar);
-      if (load_idx) bulk_load(stage_vals, src_idx + tile_base, TILE * 8, bar);
+      if (load_idx) bulk_load(stage_vals, src_idx + tile_base, TILE * 4, bar);
       arrived = mbar_wait_bounded(bar, 0);  // one thread waits; the others park at the barrier
     }
     if (!__syncthreads_and(arrived)) {
@@ -474,13 +474,13 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
     stage_keys[pos[i]]   = key[i];
   }
   if (PAIRS) {
-    int64_t val[ITEMS];
+    uint32_t val[ITEMS];
     if (load_idx) {
 #pragma unroll
       for (int i = 0; i < ITEMS; ++i) val[i] = stage_vals[stripe0 + 32 * i];
     } else {
 #pragma unroll
-      for (int i = 0; i < ITEMS; ++i) val[i] = index_offset + (int64_t)(tile_base + stripe0 + 32 * i);
+      for (int i = 0; i < ITEMS; ++i) val[i] = tile_base + stripe0 + 32 * i;
     }
     __syncthreads();  // every thread holds its indices before any slot is overwritten
 #pragma unroll
@@ -539,7 +539,8 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 
   // ---- coalesced scatter: consecutive threads store consecutive elements of a digit's run ----
   K* dst_keys       = pd.dst_keys ? static_cast<K*>(pd.dst_keys) + seg_off : nullptr;
-  int64_t* dst_idx  = pd.dst_idx ? pd.dst_idx + seg_off : nullptr;
+  uint32_t* dst_idx32 = pd.dst_idx32 ? pd.dst_idx32 + seg_off : nullptr;
+  int64_t* dst_idx64  = pd.dst_idx64 ? pd.dst_idx64 + seg_off : nullptr;
   const bool wr_key = dst_keys != nullptr;
   if (full) {
 #pragma unroll
@@ -548,7 +549,11 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
       const K k            = stage_keys[p];
       const unsigned int g = base_ml[digit_fast<KB, XF>(k, ds, shift)] + p;
       if (wr_key) __stcg(dst_keys + g, k);
-      if (PAIRS) __stcg(reinterpret_cast<long long*>(dst_idx) + g, (long long)stage_vals[p]);
+      if (PAIRS) {
+        const uint32_t v = stage_vals[p];
+        if (dst_idx64 != nullptr) __stcg(reinterpret_cast<long long*>(dst_idx64) + g, (long long)v + index_offset);
+        else __stcg(dst_idx32 + g, v);
+      }
     }
   } else {
 #pragma unroll
@@ -558,7 +563,11 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
       const unsigned int g = base_ml[digit_fast<KB, XF>(k, ds, shift)] + p;
       if (p < valid) {
         if (wr_key) dst_keys[g] = k;
-        if (PAIRS) dst_idx[g] = stage_vals[p];
+        if (PAIRS) {
+          const uint32_t v = stage_vals[p];
+          if (dst_idx64 != nullptr) dst_idx64[g] = (int64_t)v + index_offset;
+          else dst_idx32[g] = v;
+        }
       }
     }
   }
