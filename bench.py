@@ -30,7 +30,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used when MEASURE
 
 # DRAM bytes (read + write) of one onesweep launch per key, from the ncu capture summarised in
 # profiles/ (scaled to a full launch by the number of keys); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_KEY = {"c1": 7.45, "c2": 22.76}  # c2: a middle pass (reads and writes key + index)
+NCU_TRAFFIC_BYTES_PER_KEY = {"c1": 7.77, "c2": 13.8}  # c2: mean of the four passes (10.8, 14.8, 14.8, 14.7)
 
 
 def measured_hbm_peak():
