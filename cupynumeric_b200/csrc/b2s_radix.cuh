@@ -21,8 +21,14 @@ __device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], ty
 #pragma unroll
   for (int p = 0; p < KB; ++p) {
     const unsigned int d = (unsigned int)(k >> (8 * p)) & 0xFFu;
+#if B2S_HIST_FORM == 1
+    const int same = __all_sync(0xFFFFFFFFu, __shfl_sync(0xFFFFFFFFu, d, 0) == d);
+#elif B2S_HIST_FORM == 2
+    const int same = 0;
+#else
     int same;
     __match_all_sync(0xFFFFFFFFu, d, &same);
+#endif
     if (same) {
       if ((threadIdx.x & 31) == 0) atomicAdd(&sh[p][d], 32u);
     } else {
@@ -31,6 +37,9 @@ __device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], ty
   }
 }
 
+#ifndef B2S_HIST_FORM
+#define B2S_HIST_FORM 0
+#endif
 constexpr int HIST_THREADS = 512;
 
 template <int KB, int XF>
