@@ -193,7 +193,7 @@ static cudaStream_t exchange_stream()
 struct PhaseTrace {
   bool on;
   std::chrono::steady_clock::time_point t0;
-  char line[512];
+  char line[512] = {0};
   int used = 0;
   int rk = 0;
   explicit PhaseTrace(int rank) : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank), t0(std::chrono::steady_clock::now()) {}
@@ -201,8 +201,11 @@ struct PhaseTrace {
   {
     if (!on) return;
     const auto t1 = std::chrono::steady_clock::now();
-    used += std::snprintf(line + used, sizeof(line) - used, " %s=%.2f", what,
-                          std::chrono::duration<double, std::milli>(t1 - t0).count());
+    if (used < (int)sizeof(line) - 1) {
+      const int w = std::snprintf(line + used, sizeof(line) - used, " %s=%.2f", what,
+                                  std::chrono::duration<double, std::milli>(t1 - t0).count());
+      if (w > 0) used = used + w < (int)sizeof(line) ? used + w : (int)sizeof(line) - 1;
+    }
     t0 = t1;
   }
   ~PhaseTrace() { if (on) std::fprintf(stderr, "[b2s dist ms r%d]%s\n", rk, line); }
@@ -328,17 +331,20 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   Scratch mem{alloc, release, alloc_ctx, {}};
   const long long n = (long long)n_local;
   PhaseTrace trace(rank);
+  int local_status = B2S_OK;
 
   // ---- 1. local sort; indices are global positions (sort.cu:1851-1854) ----
   void* keys   = mem.get((size_t)n * kb);
   int64_t* idx = argsort ? static_cast<int64_t*>(mem.get((size_t)n * 8)) : nullptr;
   if (keys == nullptr || (argsort && idx == nullptr)) return B2S_ERR_WORKSPACE;
+  void* sort_ws = nullptr;
   if (n > 0) {
     size_t ws_bytes = 0;
     int rc = b2s_workspace_bytes(dtype, n_local, n_local, argsort, &ws_bytes);
     if (rc != B2S_OK) return rc;
     void* ws = mem.get(ws_bytes);
     if (ws == nullptr) return B2S_ERR_WORKSPACE;
+    sort_ws = ws;
     rc = b2s_local_sort(dtype, keys_in, keys, idx, n_local, n_local, global_offset, 1, 1, ws, ws_bytes, stream);
     if (rc != B2S_OK) return rc;
     if (nranks == 1) {
@@ -384,6 +390,12 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   CK_CUDA(cudaMemcpyAsync(h_samples.data(), d_samples, sizeof(Sample) * s * nranks, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
   trace.mark("local_sort+samples(sync)");
+  if (sort_ws != nullptr) {
+    // a wait inside the local sort that ran out shows up here; every rank still goes on to the
+    // collectives below so that nobody is left waiting, and the error is returned at the end
+    const int st = b2s_check_status(sort_ws, stream);
+    if (st != B2S_OK) local_status = st;
+  }
   b2s_host_select_splitters(h_samples.data(), h_samples.size(), nb, h_split.data());
   CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nb - 1), cudaMemcpyHostToDevice, stream));
 
@@ -525,6 +537,6 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
         before += h_allcuts[src * row + (size_t)(d + 1) * nph] - h_allcuts[src * row + (size_t)d * nph];
     *out_global_offset = before;
   }
-  return B2S_OK;
+  return local_status;
 }
 }
