@@ -52,7 +52,7 @@ def test_workspace_bytes_grows_with_problem(dtype):
     pairs = out.value
     item = np.dtype(dtype).itemsize
     assert small < keys_only < pairs
-    assert keys_only >= 2 * (1 << 24) * item and pairs >= keys_only + 2 * (1 << 24) * 4
+    assert keys_only >= 2 * (1 << 24) * item and pairs >= 2 * (1 << 24) * (item + 4)
 
 
 def test_workspace_bytes_rejects_bad_arguments():
