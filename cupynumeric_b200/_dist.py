@@ -92,3 +92,18 @@ def dist_sort_1d(tile: torch.Tensor, argsort: bool, global_lo: int):
     n = out_len.value
     result = raw[: n * res_dtype.itemsize].view(res_dtype)
     return result, int(out_start.value)
+
+
+def rebalance_1d(part: torch.Tensor, part_start: int, out: torch.Tensor, out_start: int) -> None:
+    """Moves the rank-ordered, variable-length parts of a distributed sort into fixed extents:
+    afterwards ``out`` holds the elements ``[out_start, out_start + len(out))`` of the global
+    sorted sequence."""
+    lib = _lib.lib()
+    assert out.is_contiguous() and part.dtype == out.dtype
+    pool = _Pool()
+    st = lib.b2s_dist_rebalance_1d(part.element_size(), part.data_ptr() if part.numel() else None, part.numel(),
+                                   int(part_start), out.data_ptr() if out.numel() else None, out.numel(),
+                                   int(out_start), nccl_comm(), dist.get_rank(), dist.get_world_size(),
+                                   ctypes.cast(pool.alloc_cb, ctypes.c_void_p), ctypes.cast(pool.free_cb, ctypes.c_void_p),
+                                   None, None, None, runtime.stream_handle())
+    _lib.check(st, "b2s_dist_rebalance_1d")

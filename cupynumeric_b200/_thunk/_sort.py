@@ -61,19 +61,16 @@ def sort_swapped(output: DeferredArray, input: DeferredArray, argsort: bool, sor
                  stable: bool) -> None:
     sort_axis = normalize_axis_index(sort_axis, input.ndim)
     last = input.ndim - 1
-    if runtime.num_procs > 1 and sort_axis == 0:
-        # the sort axis is the tiled axis: needs the N-D sample sort with rebalancing
-        # (src/cupynumeric/sort/sort.cu:799-1261), which this build does not have yet
-        raise NotImplementedError("sorting along the axis that is split over processes")
     moved = create_deferred_thunk(input.swapaxes(sort_axis, last).shape, dtype=input.dtype)
     moved.copy(input.swapaxes(sort_axis, last), deep=True)
     if argsort:
         result = create_deferred_thunk(moved.shape, dtype=output.dtype)
         sort_deferred(result, moved, argsort, stable=stable)
-        output.base = result.swapaxes(last, sort_axis).base
+        back = result.swapaxes(last, sort_axis)
     else:
         sort_deferred(moved, moved, argsort, stable=stable)
-        output.base = moved.swapaxes(last, sort_axis).base
+        back = moved.swapaxes(last, sort_axis)
+    output.base, output.global_lo, output.tiled_axis = back.base, back.global_lo, back.tiled_axis
 
 
 def sort_task(output: DeferredArray, input: DeferredArray, argsort: bool, stable: bool) -> None:
@@ -85,6 +82,9 @@ def sort_task(output: DeferredArray, input: DeferredArray, argsort: bool, stable
     state: ``need_distributed_sort == false``, ``src/cupynumeric/sort/sort.cu:1825``).
     """
     tile = input.base if input.base.is_contiguous() else input.base.contiguous()
+    if runtime.num_procs > 1 and input.ndim > 1 and input.tiled_axis == input.ndim - 1:
+        sort_split_axis(output, input, tile, argsort)
+        return
     uses_unbound_output = runtime.num_procs > 1 and input.ndim == 1
     if uses_unbound_output:
         from .._dist import dist_sort_1d
@@ -96,7 +96,26 @@ def sort_task(output: DeferredArray, input: DeferredArray, argsort: bool, stable
                           and output.base.shape == tile.shape and output.base.dtype == tile.dtype) else None
     output.base = local_sort_tile(tile, argsort, stable,
                                   index_offset=input.global_lo if input.ndim == 1 else 0, out=out)
-    output.global_lo = input.global_lo
+    output.global_lo, output.tiled_axis = input.global_lo, input.tiled_axis
+
+
+def sort_split_axis(output: DeferredArray, input: DeferredArray, tile: torch.Tensor, argsort: bool) -> None:
+    """N-D tile whose sort (last) axis is the one split over the processes: every segment is a
+    1-D array spanning the ranks.  Each segment goes through the distributed 1-D sort and is then
+    moved back into this rank's fixed extent, because the output store is bound and aligned with
+    the input (the reference: sample_sort_nccl_nd + rebalance_data,
+    ``src/cupynumeric/sort/sort.cu:1759-1773,799-1261``).  One segment at a time: meant for the
+    few long segments such a tiling produces, not for many short ones."""
+    from .._dist import dist_sort_1d, rebalance_1d
+
+    extent = tile.shape[-1]
+    rows = tile.reshape(-1, extent)
+    out = torch.empty(rows.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
+    for i in range(rows.shape[0]):
+        part, start = dist_sort_1d(rows[i], argsort, input.global_lo)
+        rebalance_1d(part, start, out[i], input.global_lo)
+    output.base = out.reshape(tile.shape)
+    output.global_lo, output.tiled_axis = input.global_lo, input.tiled_axis
 
 
 def sort_deferred(output: DeferredArray, input: DeferredArray, argsort: bool, axis: int | None = -1,

@@ -40,12 +40,14 @@ def to_numpy_dtype(dt: torch.dtype) -> np.dtype:
 
 class DeferredArray:
     def __init__(self, base: torch.Tensor | None, dtype: np.dtype | None = None,
-                 shape: tuple[int, ...] | None = None, global_lo: int = 0) -> None:
+                 shape: tuple[int, ...] | None = None, global_lo: int = 0, tiled_axis: int = 0) -> None:
         self.base = base
         self._dtype = np.dtype(dtype) if dtype is not None else to_numpy_dtype(base.dtype)
         self._shape = tuple(shape) if shape is not None else tuple(base.shape)
         # position of this tile along axis 0 of the global array (1-D: first global index held)
         self.global_lo = int(global_lo)
+        # axis along which the processes' tiles are laid out (0 unless a view swapped it away)
+        self.tiled_axis = int(tiled_axis)
 
     # ---- geometry ----
     @property
@@ -66,14 +68,22 @@ class DeferredArray:
 
     # ---- the views the sort dispatch needs ----
     def reshape(self, newshape: tuple[int, ...], order: str = "C") -> "DeferredArray":
-        return DeferredArray(self.base.contiguous().reshape(newshape), global_lo=self.global_lo)
+        """C-order reshape.  Flattening a row-tiled array keeps the tiles contiguous in the flat
+        index space, so the tile offset scales by the number of elements per row."""
+        lo = self.global_lo
+        if self.ndim > 1 and len(newshape) == 1 and self.tiled_axis == 0 and self.shape[0] > 0:
+            lo = self.global_lo * (self.size // self.shape[0])
+        return DeferredArray(self.base.contiguous().reshape(newshape), global_lo=lo)
 
     def swapaxes(self, axis1: int, axis2: int) -> "DeferredArray":
-        return DeferredArray(self.base.swapaxes(axis1, axis2), global_lo=self.global_lo)
+        a1, a2 = axis1 % max(self.ndim, 1), axis2 % max(self.ndim, 1)
+        tiled = a2 if self.tiled_axis == a1 else a1 if self.tiled_axis == a2 else self.tiled_axis
+        return DeferredArray(self.base.swapaxes(axis1, axis2), global_lo=self.global_lo, tiled_axis=tiled)
 
     def copy(self, rhs: "DeferredArray", deep: bool = True) -> None:
         """Fills this thunk with a dense row-major copy of ``rhs``."""
         self.base = rhs.base.contiguous() if not deep else rhs.base.clone(memory_format=torch.contiguous_format)
+        self.global_lo, self.tiled_axis = rhs.global_lo, rhs.tiled_axis
 
     # ---- SORT ----
     def sort(self, rhs: "DeferredArray", argsort: bool = False, axis: int | None = -1,

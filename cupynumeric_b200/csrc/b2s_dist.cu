@@ -287,6 +287,66 @@ int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int6
                     static_cast<cudaStream_t>(cuda_stream));
 }
 
+int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
+                          void* out, size_t out_len, int64_t out_global_start, void* nccl_comm, int rank,
+                          int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                          b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
+{
+  if (elem_bytes == 0 || nranks < 1 || rank < 0 || rank >= nranks || alloc == nullptr) return B2S_ERR_INVALID_ARG;
+  if ((part_len > 0 && part == nullptr) || (out_len > 0 && out == nullptr)) return B2S_ERR_INVALID_ARG;
+  if (nranks > 1 && nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  ncclComm_t comm     = static_cast<ncclComm_t>(nccl_comm);
+  Scratch mem{alloc, release, alloc_ctx, {}};
+  // every rank learns where every rank's sorted part and output extent lie in the global order
+  long long mine[4] = {(long long)part_global_start, (long long)part_len, (long long)out_global_start, (long long)out_len};
+  std::vector<long long> all((size_t)4 * nranks);
+  if (nranks == 1) {
+    std::copy(mine, mine + 4, all.begin());
+  } else {
+    long long* d_all = static_cast<long long*>(mem.get(sizeof(long long) * 4 * (nranks + 1)));
+    if (d_all == nullptr) return B2S_ERR_WORKSPACE;
+    CK_CUDA(cudaMemcpyAsync(d_all + 4 * nranks, mine, sizeof(mine), cudaMemcpyHostToDevice, stream));
+    if (barrier) barrier(barrier_ctx);
+    CK_NCCL(ncclAllGather(d_all + 4 * nranks, d_all, sizeof(mine), ncclUint8, comm, stream));
+    if (barrier) barrier(barrier_ctx);
+    CK_CUDA(cudaMemcpyAsync(all.data(), d_all, sizeof(long long) * 4 * nranks, cudaMemcpyDeviceToHost, stream));
+    CK_CUDA(cudaStreamSynchronize(stream));
+  }
+  long long parts_total = 0, outs_total = 0;
+  for (int p = 0; p < nranks; ++p) {
+    parts_total += all[4 * p + 1];
+    outs_total += all[4 * p + 3];
+  }
+  if (parts_total != outs_total) return B2S_ERR_INVALID_ARG;  // extents must tile what was sorted
+  const unsigned char* src = static_cast<const unsigned char*>(part);
+  unsigned char* dst       = static_cast<unsigned char*>(out);
+  auto overlap = [](long long a0, long long a1, long long b0, long long b1, long long* lo, long long* hi) {
+    *lo = a0 > b0 ? a0 : b0;
+    *hi = a1 < b1 ? a1 : b1;
+    return *hi > *lo;
+  };
+  const long long ps = mine[0], pe = mine[0] + mine[1], os = mine[2], oe = mine[2] + mine[3];
+  if (barrier) barrier(barrier_ctx);
+  if (nranks > 1) CK_NCCL(ncclGroupStart());
+  for (int i = 1; i < nranks; ++i) {
+    const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
+    long long lo, hi;
+    if (overlap(ps, pe, all[4 * to + 2], all[4 * to + 2] + all[4 * to + 3], &lo, &hi))
+      CK_NCCL(ncclSend(src + (size_t)(lo - ps) * elem_bytes, (size_t)(hi - lo) * elem_bytes, ncclUint8, to, comm, stream));
+    if (overlap(all[4 * from], all[4 * from] + all[4 * from + 1], os, oe, &lo, &hi))
+      CK_NCCL(ncclRecv(dst + (size_t)(lo - os) * elem_bytes, (size_t)(hi - lo) * elem_bytes, ncclUint8, from, comm, stream));
+  }
+  if (nranks > 1) CK_NCCL(ncclGroupEnd());
+  if (barrier) barrier(barrier_ctx);
+  long long lo, hi;
+  if (overlap(ps, pe, os, oe, &lo, &hi))
+    CK_CUDA(cudaMemcpyAsync(dst + (size_t)(lo - os) * elem_bytes, src + (size_t)(lo - ps) * elem_bytes,
+                            (size_t)(hi - lo) * elem_bytes, cudaMemcpyDeviceToDevice, stream));
+  CK_CUDA(cudaStreamSynchronize(stream));
+  return B2S_OK;
+}
+
 int b2s_nccl_unique_id(void* out128)
 {
   static_assert(sizeof(ncclUniqueId) == 128, "unique id size");

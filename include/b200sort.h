@@ -139,6 +139,17 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
                      void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
                      size_t* out_len, int64_t* out_global_offset, void* cuda_stream);
 
+/* Moves the parts that b2s_dist_sort_1d left on the ranks (variable lengths, rank order) into
+ * fixed extents: rank r ends up with the elements [out_global_start, out_global_start + out_len)
+ * of the globally sorted sequence in `out`.  The extents of all ranks must tile the same range the
+ * parts cover.  Every rank calls.  This is what a bound, aligned output store needs after a
+ * sample sort along a split axis; it replaces rebalance_data
+ * (src/cupynumeric/sort/sort.cu:799-1261) for one segment at a time.  Synchronises the stream. */
+int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
+                          void* out, size_t out_len, int64_t out_global_start, void* nccl_comm, int rank,
+                          int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                          b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream);
+
 /* Stable merge of `nruns` (<= 32) sorted runs, ties taken from the lower-numbered run first:
  * out receives the merged keys, or - when run_idx is not NULL - only the merged int64 payloads.
  * `ws`: b2s_kway_merge_workspace_bytes(total, nruns) bytes of device scratch.  This is the last

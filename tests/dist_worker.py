@@ -21,6 +21,31 @@ def main():
     from cupynumeric_b200 import workloads as w
     from cupynumeric_b200._dist import destroy_comm
 
+    if workload == "split2d":
+        # a (world*300, 7) int32 array tiled by rows; sort along axis 0 (the tiled axis) and flat
+        rng = np.random.default_rng(100 + rank)
+        block = rng.integers(-1000, 1000, (300, 7)).astype(np.int32)
+        blocks = [None] * world
+        dist.all_gather_object(blocks, block)
+        whole = np.concatenate(blocks)
+        arr = num.array(block, global_lo=rank * 300)
+        got_s = num.sort(arr, axis=0).to_numpy()
+        got_a = num.argsort(arr, axis=0, kind="stable").to_numpy()
+        want_s, want_a = np.sort(whole, axis=0, kind="stable"), np.argsort(whole, axis=0, kind="stable")
+        assert np.array_equal(got_s, want_s[rank * 300:(rank + 1) * 300]), "sort along the split axis"
+        assert np.array_equal(got_a, want_a[rank * 300:(rank + 1) * 300]), "argsort along the split axis"
+        flat = num.sort(arr, axis=None)
+        parts = [None] * world
+        dist.all_gather_object(parts, flat.to_numpy())
+        assert np.array_equal(np.concatenate(parts), np.sort(whole, axis=None, kind="stable")), "flattened sort"
+        rows = num.sort(arr, axis=1).to_numpy()
+        assert np.array_equal(rows, np.sort(block, axis=1))
+        dist.barrier()
+        if rank == 0:
+            print("DIST_OK split2d")
+        destroy_comm()
+        dist.destroy_process_group()
+        return
     if workload == "c4":
         shard, argsort = w.c4_int64_zipf_shard(n, rank), False
     elif workload == "c5":

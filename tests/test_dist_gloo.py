@@ -139,41 +139,64 @@ def test_two_rank_sample_sort_over_gloo(kind, n, argsort):
 
 
 def rows_worker(rank: int, world: int, port: int, ret):
-    """N-D arrays are tiled by rows: every rank sorts its own row block with no exchange; sorting
-    along the tiled axis is refused.  The point task is played by the oracle."""
+    """N-D arrays are tiled by rows: a sort along the last axis is local to every rank; a sort
+    along the tiled axis makes every column a 1-D array spanning the ranks, which goes through
+    the distributed sort and the move back into fixed extents.  The point task is played by the
+    oracle, the two distributed calls by gloo stand-ins with the same contracts."""
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
+        import cupynumeric_b200._dist as dist_mod
         from cupynumeric_b200._thunk import _sort as sort_mod
         from cupynumeric_b200._thunk.deferred import DeferredArray, create_deferred_thunk
         from cupynumeric_b200.runtime import runtime
         from oracle import np_task_sort
 
-        def fake(tile, argsort, stable, index_offset=0, out=None):
+        def fake_local(tile, argsort, stable, index_offset=0, out=None):
             a = tile.numpy()
             res = np_task_sort(a, a.shape[-1], argsort, index_offset=index_offset, ndim_is_1=a.ndim == 1)
             return torch.from_numpy(np.ascontiguousarray(res.reshape(a.shape)))
 
-        sort_mod.local_sort_tile = fake
+        def fake_dist_sort(tile, argsort, global_lo):
+            """Same contract as dist_sort_1d: returns (this rank's part, its global start); the
+            parts are deliberately uneven."""
+            shards = [None] * world
+            dist.all_gather_object(shards, tile.numpy().copy())
+            whole = np.concatenate(shards)
+            res = np.argsort(whole, kind="stable").astype(np.int64) if argsort else np.sort(whole, kind="stable")
+            cut = [0, max(1, whole.size // 3), whole.size][rank:rank + 2]
+            return torch.from_numpy(res[cut[0]:cut[1]].copy()), cut[0]
+
+        def fake_rebalance(part, part_start, out, out_start):
+            parts = [None] * world
+            dist.all_gather_object(parts, (int(part_start), part.numpy().copy()))
+            whole = np.concatenate([p for _, p in sorted(parts, key=lambda t: t[0])])
+            out.copy_(torch.from_numpy(whole[out_start:out_start + out.numel()].copy()))
+
+        sort_mod.local_sort_tile = fake_local
+        dist_mod.dist_sort_1d = fake_dist_sort
+        dist_mod.rebalance_1d = fake_rebalance
         assert runtime.num_procs == world
         whole = np.random.default_rng(9).integers(-50, 50, (8, 13)).astype(np.int32)
         block = whole[rank * 4:(rank + 1) * 4]
         out = create_deferred_thunk(block.shape, np.int64)
         out.sort(DeferredArray(torch.from_numpy(block.copy()), global_lo=rank * 4), argsort=True, axis=-1, kind="stable")
-        ok = bool(np.array_equal(out.base.numpy(), np.argsort(block, axis=-1, kind="stable")))
-        refused = False
-        try:
-            out.sort(DeferredArray(torch.from_numpy(block.copy()), global_lo=rank * 4), axis=0)
-        except NotImplementedError:
-            refused = True
-        ret.put((rank, ok, refused))
+        ok_rows = bool(np.array_equal(out.base.numpy(), np.argsort(block, axis=-1, kind="stable")))
+        ok_split = True
+        for argsort in (False, True):
+            res = create_deferred_thunk(block.shape, np.int64 if argsort else np.int32)
+            res.sort(DeferredArray(torch.from_numpy(block.copy()), global_lo=rank * 4), argsort=argsort, axis=0, kind="stable")
+            want = (np.argsort(whole, axis=0, kind="stable") if argsort else np.sort(whole, axis=0, kind="stable"))
+            ok_split &= bool(np.array_equal(res.base.numpy(), want[rank * 4:(rank + 1) * 4]))
+            ok_split &= res.global_lo == rank * 4 and res.tiled_axis == 0
+        ret.put((rank, ok_rows, ok_split))
     finally:
         dist.destroy_process_group()
 
 
-def test_row_blocks_sort_locally_and_tiled_axis_is_refused():
+def test_row_blocks_sort_locally_and_split_axis_goes_distributed():
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = 31500 + os.getpid() % 2000
