@@ -2,7 +2,7 @@
 behind ``sort``, ``argsort`` and ``ndarray.sort`` - behind a C ABI (``include/b200sort.h``),
 with the host-side dispatch of the reference's Python layer on top."""
 from ._array import array, ndarray  # noqa: F401
-from ._module.ssc_sorting import argsort, sort  # noqa: F401
+from ._module.ssc_sorting import argsort, searchsorted, sort  # noqa: F401
 from .runtime import runtime  # noqa: F401
 
-__all__ = ["array", "ndarray", "sort", "argsort", "runtime"]
+__all__ = ["array", "ndarray", "sort", "argsort", "searchsorted", "runtime"]

@@ -102,6 +102,37 @@ class DeferredArray:
         sort_deferred(self, rhs, argsort, axis, stable)
 
 
+    def searchsorted(self, rhs: "DeferredArray", v: "DeferredArray", side: str = "left") -> None:
+        """Fills this int64 thunk (shaped like ``v``) with insertion positions of ``v`` in the
+        sorted 1-D array ``rhs`` whose tiles may span the processes.  Follows
+        ``DeferredArray.searchsorted`` (``cupynumeric/_thunk/deferred.py:5425-5451``): pre-fill
+        with ``rhs`` global size (left) or 0 (right), per-tile contributions, MIN / MAX over
+        ranks.  ``v`` is the same on every process (broadcast constraint of the reference)."""
+        import torch.distributed as dist
+
+        from .. import _lib
+
+        lib = _lib.lib()
+        is_left = side == "left"
+        tile = rhs.base.contiguous()
+        vals = v.base.contiguous()
+        assert vals.dtype == tile.dtype, "searchsorted: the caller brings both arrays to one dtype"
+        global_size = tile.numel()
+        if runtime.num_procs > 1:
+            t = torch.tensor([global_size], dtype=torch.int64, device=tile.device)
+            dist.all_reduce(t)
+            global_size = int(t.item())
+        out = torch.full(vals.shape, global_size if is_left else 0, dtype=torch.int64, device=tile.device)
+        _lib.check(lib.b2s_searchsorted(_lib.DTYPE_CODE[to_numpy_dtype(tile.dtype)],
+                                        tile.data_ptr() if tile.numel() else None, tile.numel(), rhs.global_lo,
+                                        vals.data_ptr() if vals.numel() else None, vals.numel(), int(is_left),
+                                        out.data_ptr() if out.numel() else None, runtime.stream_handle()),
+                   "b2s_searchsorted")
+        if runtime.num_procs > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.MIN if is_left else dist.ReduceOp.MAX)
+        self.base = out
+
+
 def create_deferred_thunk(shape: tuple[int, ...], dtype: Any) -> DeferredArray:
     """An output thunk whose device memory is attached by the task that fills it."""
     return DeferredArray(None, dtype=np.dtype(dtype), shape=tuple(shape))

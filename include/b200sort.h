@@ -181,6 +181,19 @@ int b2s_host_select_splitters(void* samples, size_t count, int nranks, void* spl
  * counts of local keys below / not above the splitter's key (sort.cu:170-187). */
 long long b2s_host_cut_position(const void* splitter, int my_rank, long long lower, long long upper);
 
+/* ---- SEARCHSORTED (the sorted output's natural consumer; a separate task in the reference) ---- */
+
+/* For each of `num_values` values, combines this tile's contribution to its insertion position
+ * in the global sorted array into `positions` (int64, one per value): left != 0 -> atomic MIN of
+ * (lower bound + global_offset) when the lower bound lies inside the tile; left == 0 -> atomic
+ * MAX of (upper bound + global_offset) when it is positive.  The caller pre-fills `positions`
+ * with the global array size (left) or 0 (right) and reduces over ranks with MIN / MAX, exactly
+ * the reduction stores of the reference task (src/cupynumeric/sort/searchsorted.cu:25-122,
+ * cupynumeric/_thunk/deferred.py:5425-5451).  Keys compare in the sort's total order. */
+int b2s_searchsorted(int dtype, const void* sorted_tile, size_t n_tile, int64_t global_offset,
+                     const void* values, size_t num_values, int left, int64_t* positions,
+                     void* cuda_stream);
+
 /* ---- measurement aids (no counterpart in the reference, which relies on Legate's profiler,
  * cupynumeric/_utils/profiling.py:33-73) ------------------------------------------------------ */
 

@@ -21,6 +21,23 @@ def main():
     from cupynumeric_b200 import workloads as w
     from cupynumeric_b200._dist import destroy_comm
 
+    if workload == "search":
+        # sort across the ranks, then look values up in the distributed result
+        shard = np.random.default_rng(50 + rank).integers(-10_000, 10_000, 200_000).astype(np.int64)
+        shards = [None] * world
+        dist.all_gather_object(shards, shard)
+        whole = np.sort(np.concatenate(shards), kind="stable")
+        srt = num.sort(num.array(shard, global_lo=rank * shard.size))
+        v = np.random.default_rng(7).integers(-11_000, 11_000, 5000).astype(np.int64)   # same on every rank
+        for side in ("left", "right"):
+            got = num.searchsorted(srt, v, side=side).to_numpy()
+            assert np.array_equal(got, np.searchsorted(whole, v, side=side)), side
+        dist.barrier()
+        if rank == 0:
+            print("DIST_OK search")
+        destroy_comm()
+        dist.destroy_process_group()
+        return
     if workload == "split2d":
         # a (world*300, 7) int32 array tiled by rows; sort along axis 0 (the tiled axis) and flat
         rng = np.random.default_rng(100 + rank)
