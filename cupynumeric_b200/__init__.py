@@ -2,7 +2,9 @@
 behind ``sort``, ``argsort`` and ``ndarray.sort`` - behind a C ABI (``include/b200sort.h``),
 with the host-side dispatch of the reference's Python layer on top."""
 from ._array import array, ndarray  # noqa: F401
-from ._module.ssc_sorting import argsort, searchsorted, sort  # noqa: F401
+from ._module.ssc_sorting import (argpartition, argsort, lexsort, partition, searchsorted, sort,  # noqa: F401
+                                  sort_complex)
 from .runtime import runtime  # noqa: F401
 
-__all__ = ["array", "ndarray", "sort", "argsort", "searchsorted", "runtime"]
+__all__ = ["array", "ndarray", "sort", "argsort", "searchsorted", "sort_complex", "partition", "argpartition",
+           "lexsort", "runtime"]
