@@ -105,6 +105,8 @@ SIGNATURES = {
     "b2s_host_select_splitters": (_I, [_P, _SZ, _I, _P]),
     "b2s_host_cut_position": (ctypes.c_longlong, [_P, _I, ctypes.c_longlong, ctypes.c_longlong]),
     "b2s_searchsorted": (_I, [_I, _P, _SZ, _I64, _P, _SZ, _I, _P, _P]),
+    "b2s_unique_workspace_bytes": (_I, [_SZ, ctypes.POINTER(_SZ)]),
+    "b2s_unique_sorted": (_I, [_I, _P, _SZ, _P, ctypes.POINTER(_SZ), _P, _SZ, _P]),
     "b2s_profile_enable": (_I, [_I]),
     "b2s_profile_read": (_I, [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_ulonglong)]),
     "b2s_launch_count": (ctypes.c_ulonglong, [_I]),

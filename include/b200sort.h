@@ -194,6 +194,18 @@ int b2s_searchsorted(int dtype, const void* sorted_tile, size_t n_tile, int64_t 
                      const void* values, size_t num_values, int left, int64_t* positions,
                      void* cuda_stream);
 
+/* ---- UNIQUE on sorted data ------------------------------------------------------------------- */
+
+/* Writes the first element of every run of equal keys of `sorted` (n elements, ascending) to
+ * `out` (room for n elements, must not alias `sorted`) and the number written to *out_len.
+ * Keys are equal when the sort treats them as ties: one NaN, one zero.  After b2s_local_sort
+ * this is the local half of the reference's UNIQUE task (thrust::sort + thrust::unique,
+ * src/cupynumeric/set/unique.cu:150-208).  `ws`: b2s_unique_workspace_bytes(n) bytes, 256-byte
+ * aligned.  Synchronises the stream (the count comes back to the host). */
+int b2s_unique_workspace_bytes(size_t n, size_t* bytes);
+int b2s_unique_sorted(int dtype, const void* sorted, size_t n, void* out, size_t* out_len, void* ws,
+                      size_t ws_bytes, void* cuda_stream);
+
 /* ---- measurement aids (no counterpart in the reference, which relies on Legate's profiler,
  * cupynumeric/_utils/profiling.py:33-73) ------------------------------------------------------ */
 

@@ -32,6 +32,13 @@ def main():
         for side in ("left", "right"):
             got = num.searchsorted(srt, v, side=side).to_numpy()
             assert np.array_equal(got, np.searchsorted(whole, v, side=side)), side
+        # unique across the ranks: parts are sorted, disjoint and in rank order
+        few = np.random.default_rng(60 + rank).integers(0, 50, 100_000).astype(np.int64)
+        fews = [None] * world
+        dist.all_gather_object(fews, few)
+        uparts = [None] * world
+        dist.all_gather_object(uparts, num.unique(num.array(few, global_lo=rank * few.size)).to_numpy())
+        assert np.array_equal(np.concatenate(uparts), np.unique(np.concatenate(fews))), "distributed unique"
         dist.barrier()
         if rank == 0:
             print("DIST_OK search")

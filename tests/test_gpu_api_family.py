@@ -50,3 +50,26 @@ def test_lexsort(cuda_device):
         num.lexsort((k1, k2), axis=None)
     with pytest.raises(ValueError):
         num.lexsort((k1, k2[:10]))
+
+
+def test_unique(cuda_device):
+    rng = np.random.default_rng(4)
+    dtypes = [np.bool_, np.int8, np.int16, np.int32, np.int64, np.uint8, np.uint16, np.uint32, np.uint64,
+              np.float16, np.float32, np.float64]
+    for dtype in dtypes:
+        for n in (0, 1, 5, 4096, 4097, 300_000):
+            raw = rng.integers(-40, 40, n)
+            a = (np.abs(raw) if np.dtype(dtype).kind in "ub" else raw).astype(dtype)
+            if np.dtype(dtype).kind == "f" and n > 4:
+                a[::5] = np.nan
+                a[1::7] = -0.0
+                a[2::7] = 0.0
+            got = num.unique(a).to_numpy()
+            want = np.unique(a)
+            assert got.shape == want.shape and np.array_equal(got, want, equal_nan=np.dtype(dtype).kind == "f"), (dtype, n)
+    m = rng.integers(0, 10, (30, 40)).astype(np.int32)
+    assert np.array_equal(num.unique(m).to_numpy(), np.unique(m))
+    with pytest.raises(NotImplementedError):
+        num.unique(m, return_counts=True)
+    with pytest.raises(NotImplementedError):
+        num.unique(m, axis=0)
