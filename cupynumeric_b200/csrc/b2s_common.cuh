@@ -6,6 +6,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// float32 digit extraction through one floating-point add (see to_ordered)
+#ifndef B2S_FLOAT_FADD
+#define B2S_FLOAT_FADD 2
+#endif
+
 namespace b2s {
 
 // ---------------------------------------------------------------------------------------------
@@ -42,6 +47,24 @@ __host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered(typename
   } else {
     // exponent mask: all exponent bits set = inf/NaN
     constexpr K EXP = (KB == 2) ? (K)0x7C00u : (KB == 4) ? (K)0x7F800000u : (K)0x7FF0000000000000ull;
+#if defined(__CUDA_ARCH__) && B2S_FLOAT_FADD
+    if (KB == 4) {
+      // float32 on the device: adding +0.0 turns -0.0 into +0.0 and leaves every other value
+      // (denormals included) as it is; then the usual sign flip, and NaNs to all-ones.
+      const float f        = __uint_as_float((unsigned int)raw);
+      const unsigned int u = __float_as_uint(f + 0.0f);
+      const unsigned int m = (unsigned int)((int)u >> 31) | 0x80000000u;
+      return (K)(f != f ? 0xFFFFFFFFu : (u ^ m));
+    }
+#if B2S_FLOAT_FADD >= 2
+    if (KB == 8) {
+      const double f             = __longlong_as_double((long long)raw);
+      const unsigned long long u = (unsigned long long)__double_as_longlong(f + 0.0);
+      const unsigned long long m = (unsigned long long)((long long)u >> 63) | 0x8000000000000000ull;
+      return (K)(f != f ? ~0ull : (u ^ m));
+    }
+#endif
+#endif
     // straight-line selects: branches here would diverge inside the per-key loops
     const K mag  = (K)(raw & (K)~SB);
     const K mask = (raw & SB) ? (K)~(K)0 : SB;   // negative: flip everything; positive: set the sign
