@@ -53,11 +53,12 @@ def make_workload(name: str, rank: int, nranks: int, scale_log2: int | None):
 
     if name == "c1":
         n = 1 << (scale_log2 or 24)
-        return dict(keys=w.c1_int32_uniform(n), argsort=False, label=f"1-D int32 sort, N=2^{n.bit_length()-1}, uniform full range, seed 101",
+        return dict(keys=w.c1_int32_uniform(n, seed=101 + rank), argsort=False, label=f"1-D int32 sort, N=2^{n.bit_length()-1}, uniform full range, seed 101",
                     bytes_per_key=36.0, sweep_bytes_per_key=8.0, dtype="i32")
     if name == "c2":
         n = 1 << (scale_log2 or 28)
-        return dict(keys=w.c2_float32_nan_dups(n), argsort=True,
+        # rank 0 holds the configuration's own array; further ranks draw fresh shards of the same distribution
+        return dict(keys=w.c2_float32_nan_dups(n, seed=202 + rank), argsort=True,
                     label=f"1-D float32 stable argsort -> int64, N=2^{n.bit_length()-1}, N(0,1) + 0.1% NaN + 1% duplicates, seed 202",
                     bytes_per_key=88.0, sweep_bytes_per_key=21.0, dtype="f32")
     if name == "c3":
