@@ -159,12 +159,16 @@ template <int KB, bool ARGS, bool FLT>
 struct MergeSmem {
   static constexpr bool SLOTS = ARGS || FLT;
   static constexpr bool RAW   = FLT && !ARGS;
+  // keys of at most 32 bits share a 64-bit word with their slot: (ordered key << 32) | slot.
+  // Comparing the words orders by key, then by slot, which is run order: the merge stays stable
+  // and needs no separate slot arrays.
+  static constexpr bool PACK  = SLOTS && KB <= 4;
   static constexpr size_t OFF_RAW  = 0;
   static constexpr size_t OFF_OK0  = (RAW ? ((size_t)MERGE_TILE * KB + 15) / 16 * 16 : 0);
   static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_PADDED * 8;
   static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_PADDED * 8;
-  static constexpr size_t OFF_SL1  = OFF_SL0 + (SLOTS ? (size_t)MERGE_PADDED * 2 : 0);
-  static constexpr size_t OFF_BND  = (OFF_SL1 + (SLOTS ? (size_t)MERGE_PADDED * 2 : 0) + 15) / 16 * 16;
+  static constexpr size_t OFF_SL1  = OFF_SL0 + ((SLOTS && !PACK) ? (size_t)MERGE_PADDED * 2 : 0);
+  static constexpr size_t OFF_BND  = (OFF_SL1 + ((SLOTS && !PACK) ? (size_t)MERGE_PADDED * 2 : 0) + 15) / 16 * 16;
   static constexpr size_t OFF_SRC  = (OFF_BND + (MERGE_MAX_RUNS + 1) * 4 + 15) / 16 * 16;  // 8-byte entries
   static constexpr size_t OFF_KP   = OFF_SRC + MERGE_MAX_RUNS * 8;   // run key pointers
   static constexpr size_t OFF_IP   = OFF_KP + MERGE_MAX_RUNS * 8;    // run payload pointers
@@ -188,7 +192,8 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
 {
   using K = typename KeyOf<KB>::type;
   using S = MergeSmem<KB, ARGS, FLT>;
-  constexpr bool SLOTS = S::SLOTS;
+  constexpr bool PACK  = S::PACK;
+  constexpr bool SLOTS = S::SLOTS && !PACK;  // separate slot arrays
   constexpr bool RAW   = S::RAW;
   extern __shared__ __align__(16) unsigned char smem[];
   K* raw                    = reinterpret_cast<K*>(smem + S::OFF_RAW);
@@ -234,7 +239,8 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     for (int q = q0 + tid; q < q1; q += MERGE_THREADS) {
       const K k = kp[q - q0];
       if (RAW) raw[q] = k;
-      ok[0][mpad(q)] = (unsigned long long)to_ordered_rt<KB>(k, xf);
+      const unsigned long long o = (unsigned long long)to_ordered_rt<KB>(k, xf);
+      ok[0][mpad(q)] = PACK ? ((o << 32) | (unsigned long long)q) : o;
       if (SLOTS) sl[0][mpad(q)] = (unsigned short)q;
     }
   }
@@ -287,7 +293,9 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     __syncthreads();
   }
 
-  const unsigned short* fs = sl[cur];
+  const unsigned short* fs     = sl[cur];
+  const unsigned long long* fp = ok[cur];
+  auto slot_of = [&](int q) -> unsigned int { return PACK ? (unsigned int)(fp[mpad(q)] & 0xFFFFu) : (unsigned int)fs[mpad(q)]; };
   if (ARGS) {
     // the merge buffer that is no longer read becomes the payload staging area
     int64_t* pay = reinterpret_cast<int64_t*>(ok[cur ^ 1]);
@@ -298,10 +306,10 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     }
     __syncthreads();
     int64_t* o = static_cast<int64_t*>(out) + base;
-    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[fs[mpad(q)]];
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = pay[slot_of(q)];
   } else if (RAW) {
     K* o = static_cast<K*>(out) + base;
-    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[fs[mpad(q)]];
+    for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[slot_of(q)];
   } else {
     K* o                         = static_cast<K*>(out) + base;
     const unsigned long long* fk = ok[cur];
