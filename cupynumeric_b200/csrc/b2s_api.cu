@@ -42,13 +42,13 @@ inline size_t radix_ws(int kb, size_t n, bool pairs)
 }
 
 inline cudaError_t radix_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int n,
-                             int64_t off, unsigned char* ws, cudaStream_t s)
+                             int64_t off, unsigned char* ws, cudaStream_t s, int idx32 = 0)
 {
   switch (kb) {
-    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s);
-    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s);
-    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s);
-    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s);
+    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s, idx32);
+    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s, idx32);
+    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s, idx32);
+    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s, idx32);
   }
 }
 
@@ -139,6 +139,27 @@ inline int chunk_layout(int dtype, int kb, size_t n, bool argsort, ChunkLayout* 
   l->off_cuts = off; off += align_up(l->cuts_bytes, 256);
   l->total = off;
   return B2S_OK;
+}
+
+
+// Stable 1-D argsort that leaves 32-bit positions 0..n-1 instead of int64 global indices: the
+// distributed sort ships these through the exchange (4 bytes per element instead of 8) and adds
+// the source rank's offset after the merge.  Only for sizes the single radix sort takes.
+bool local_sort_pos32_supported(size_t n) { return n > SEG_CAP && n < single_sort_limit(); }
+
+int local_sort_pos32(int dtype, const void* keys_in, void* keys_out, uint32_t* pos_out, size_t n, void* ws,
+                     size_t ws_bytes, cudaStream_t stream)
+{
+  DtypeInfo di;
+  if (!dtype_info(dtype, &di) || !local_sort_pos32_supported(n)) return B2S_ERR_UNSUPPORTED;
+  if (keys_in == nullptr || keys_out == nullptr || pos_out == nullptr) return B2S_ERR_INVALID_ARG;
+  size_t need = 0;
+  int rc      = b2s_workspace_bytes(dtype, n, n, 1, &need);
+  if (rc != B2S_OK) return rc;
+  if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
+  const cudaError_t e = radix_any(di.kb, di.xf, keys_in, keys_out, reinterpret_cast<int64_t*>(pos_out), (unsigned int)n, 0,
+                                  static_cast<unsigned char*>(ws), stream, 1);
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 
 }  // namespace b2s

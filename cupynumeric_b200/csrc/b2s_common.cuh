@@ -117,7 +117,7 @@ struct FixDesc {
   void* copy_dst;
   unsigned long long copy_bytes;
   int64_t* synth_idx;    // non-null: write index_offset + i
-  int pad_[2];
+  uint32_t* synth_idx32; // non-null: write i
 };
 
 struct Ctrl {

@@ -15,6 +15,13 @@
 
 #include "../../include/b200sort.h"
 #include "b2s_common.cuh"
+
+namespace b2s {
+// defined with the local sort
+bool local_sort_pos32_supported(size_t n);
+int local_sort_pos32(int dtype, const void* keys_in, void* keys_out, uint32_t* pos_out, size_t n, void* ws,
+                     size_t ws_bytes, cudaStream_t stream);
+}  // namespace b2s
 #include "b2s_dist_host.h"
 #include "b2s_merge.cuh"
 #include "b2s_prof.h"
@@ -66,7 +73,7 @@ __global__ void sample_kernel(const void* sorted, long long n, int s, int rank, 
 // cuts[k] for k = 1..nranks-1: how many of my sorted elements go to ranks < k.
 template <int KB>
 __global__ void cut_kernel(const void* sorted, long long n, const Sample* splitters, int nranks, int rank,
-                           int xf, long long* cuts)
+                           int xf, long long* cuts, long long tag0, long long tag1)
 {
   const int k = blockIdx.x * blockDim.x + threadIdx.x + 1;
   if (k >= nranks) return;
@@ -81,8 +88,10 @@ __global__ void cut_kernel(const void* sorted, long long n, const Sample* splitt
   }
   cuts[k] = c;
   if (k == 1) {
-    cuts[0]      = 0;
-    cuts[nranks] = n;
+    cuts[0]          = 0;
+    cuts[nranks]     = n;
+    cuts[nranks + 1] = tag0;  // two words that travel with the cuts to every rank
+    cuts[nranks + 2] = tag1;
   }
 }
 
@@ -128,6 +137,15 @@ struct Scratch {
 };
 
 // Launches the partition and merge kernels for `runs` (total elements) into `out`.
+// probes per search step (minus one) in the two partition launches: the coarse one has few,
+// long searches and is pure latency; the fine one has many short ones
+#ifndef B2S_PART_ARY_COARSE
+#define B2S_PART_ARY_COARSE 8
+#endif
+#ifndef B2S_PART_ARY_FINE
+#define B2S_PART_ARY_FINE 2
+#endif
+
 static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bool args, void* out,
                       long long* d_tcuts, cudaStream_t stream)
 {
@@ -140,7 +158,7 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
       int gw = 1;
       while (gw < runs.nruns) gw <<= 1;
       const long long per_cta = 8 * (32 / gw);  // boundaries per CTA of 8 warps
-      merge_partition_kernel<KB><<<(unsigned int)((ncoarse + per_cta - 1) / per_cta), 256, 0, stream>>>(
+      merge_partition_kernel<KB, B2S_PART_ARY_COARSE><<<(unsigned int)((ncoarse + per_cta - 1) / per_cta), 256, 0, stream>>>(
         runs, total, ntiles, xf, d_tcuts, MERGE_COARSE_STRIDE, 0);
     }
     {
@@ -149,7 +167,7 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
       int gw = 1;
       while (gw < runs.nruns) gw <<= 1;
       const long long per_cta = 8 * (32 / gw);
-      merge_partition_kernel<KB><<<(unsigned int)((warps + per_cta - 1) / per_cta), 256, 0, stream>>>(
+      merge_partition_kernel<KB, B2S_PART_ARY_FINE><<<(unsigned int)((warps + per_cta - 1) / per_cta), 256, 0, stream>>>(
         runs, total, ntiles, xf, d_tcuts, MERGE_COARSE_STRIDE, 1);
     }
     prof::Scope ps(prof::K_MERGE, stream);
@@ -273,7 +291,9 @@ int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int6
   long long total = 0;
   for (int i = 0; i < nruns; ++i) {
     runs.keys[i] = run_keys[i];
-    runs.idx[i]  = run_idx ? run_idx[i] : nullptr;
+    runs.idx[i]       = run_idx ? run_idx[i] : nullptr;
+    runs.idx_bytes[i] = 8;
+    runs.idx_base[i]  = 0;
     runs.len[i]  = (long long)run_len[i];
     if (run_len[i] > 0 && (run_keys[i] == nullptr || (run_idx && run_idx[i] == nullptr))) return B2S_ERR_INVALID_ARG;
     total += runs.len[i];
@@ -394,8 +414,13 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   int local_status = B2S_OK;
 
   // ---- 1. local sort; indices are global positions (sort.cu:1851-1854) ----
-  void* keys   = mem.get((size_t)n * kb);
-  int64_t* idx = argsort ? static_cast<int64_t*>(mem.get((size_t)n * 8)) : nullptr;
+  // With more than one rank an argsort carries 32-bit local positions through the exchange where
+  // the local sort can produce them; the merge adds the source rank's offset.  Each rank tells
+  // the others which form it sends (payload width and offset travel with the cut positions).
+  const bool pos32 = argsort && nranks > 1 && local_sort_pos32_supported(n_local);
+  const size_t pb  = pos32 ? 4 : 8;  // bytes per payload element I send
+  void* keys       = mem.get((size_t)n * kb);
+  unsigned char* idx = argsort ? static_cast<unsigned char*>(mem.get((size_t)n * pb)) : nullptr;
   if (keys == nullptr || (argsort && idx == nullptr)) return B2S_ERR_WORKSPACE;
   void* sort_ws = nullptr;
   if (n > 0) {
@@ -405,7 +430,11 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     void* ws = mem.get(ws_bytes);
     if (ws == nullptr) return B2S_ERR_WORKSPACE;
     sort_ws = ws;
-    rc = b2s_local_sort(dtype, keys_in, keys, idx, n_local, n_local, global_offset, 1, 1, ws, ws_bytes, stream);
+    if (pos32)
+      rc = local_sort_pos32(dtype, keys_in, keys, reinterpret_cast<uint32_t*>(idx), n_local, ws, ws_bytes, stream);
+    else
+      rc = b2s_local_sort(dtype, keys_in, keys, reinterpret_cast<int64_t*>(idx), n_local, n_local, global_offset, 1, 1,
+                          ws, ws_bytes, stream);
     if (rc != B2S_OK) return rc;
     if (nranks == 1) {
       rc = b2s_check_status(ws, stream);
@@ -415,7 +444,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     if (nranks == 1) mem.drop(ws);
   }
   if (nranks == 1) {
-    void* result = argsort ? static_cast<void*>(idx) : keys;
+    void* result = argsort ? static_cast<void*>(idx) : keys;  // one rank: idx holds int64 global indices
     mem.disown(result);
     *out_ptr = result;
     *out_len = n_local;
@@ -432,8 +461,8 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   const int s        = SAMPLES_PER_RANK;
   Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
   Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nb));
-  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 1)));
-  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 1)));
+  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 3)));
+  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 3)));
   if (!d_samples || !d_split || !d_cuts || !d_count) return B2S_ERR_WORKSPACE;
   {
     prof::Scope ps(prof::K_DIST, stream);
@@ -463,12 +492,13 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   {
     prof::Scope ps(prof::K_DIST, stream);
     by_width(kb, [&](auto w) {
-      cut_kernel<decltype(w)::value><<<(nb + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nb, rank, xf, d_cuts);
+      cut_kernel<decltype(w)::value><<<(nb + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nb, rank, xf, d_cuts,
+                                                                        (long long)pb, (long long)global_offset);
       return cudaSuccess;
     });
   }
   CK_CUDA(cudaGetLastError());
-  const size_t row = (size_t)nb + 1;
+  const size_t row = (size_t)nb + 3;  // nb + 1 cut positions, payload width, global offset
   std::vector<long long> h_allcuts((size_t)nranks * row);
   if (barrier) barrier(barrier_ctx);
   CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * row, ncclUint8, comm, stream));
@@ -479,6 +509,12 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   for (int src = 0; src < nranks; ++src)
     for (int q = 0; q < nb; ++q)
       if (h_allcuts[src * row + q] > h_allcuts[src * row + q + 1]) return B2S_ERR_INVALID_ARG;  // protocol mismatch
+  std::vector<size_t> pay_bytes(nranks);
+  for (int src = 0; src < nranks; ++src) {
+    const long long w = h_allcuts[src * row + nb + 1];
+    if (w != 4 && w != 8) return B2S_ERR_INVALID_ARG;
+    pay_bytes[src] = (size_t)w;
+  }
   const long long* my_cuts = &h_allcuts[(size_t)rank * row];
 
   // ---- 4. exchange and merge, phase by phase ----
@@ -507,14 +543,17 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     total += ph_total[ph];
   }
   unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)slots * kb));
-  int64_t* r_idx        = argsort ? static_cast<int64_t*>(mem.get((size_t)slots * 8)) : nullptr;
+  unsigned char* r_idx  = argsort ? static_cast<unsigned char*>(mem.get((size_t)slots * 8)) : nullptr;
   void* result          = mem.get((size_t)total * (argsort ? 8 : kb));
   if (r_keys == nullptr || (argsort && r_idx == nullptr) || result == nullptr) return B2S_ERR_WORKSPACE;
   std::vector<void*> tcuts(nph, nullptr);
   for (int ph = 0; ph < nph; ++ph) {
     for (int p = 0; p < nranks; ++p) {
       runs[ph].keys[p] = r_keys + (size_t)(recv_off[ph][p] + lead[ph][p]) * kb;
-      runs[ph].idx[p]  = argsort ? r_idx + recv_off[ph][p] + lead[ph][p] : nullptr;
+      // a run's payload sits at the same element offset as its keys, whatever its width
+      runs[ph].idx[p]      = argsort ? r_idx + (size_t)recv_off[ph][p] * 8 + (size_t)lead[ph][p] * pay_bytes[p] : nullptr;
+      runs[ph].idx_bytes[p] = (int)pay_bytes[p];
+      runs[ph].idx_base[p]  = pay_bytes[p] == 4 ? h_allcuts[p * row + nb + 2] : 0;
     }
     if (ph_total[ph] > 0) {
       size_t mws = 0;
@@ -546,12 +585,13 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
         const long long a0 = c0 - c0 % XFER_ALIGN;
         const size_t cnt   = (size_t)(c1 - a0);
         CK_NCCL(ncclSend(k_bytes + (size_t)a0 * kb, cnt * kb, ncclUint8, to, comm, xs));
-        if (argsort) CK_NCCL(ncclSend(idx + a0, cnt, ncclInt64, to, comm, xs));
+        if (argsort) CK_NCCL(ncclSend(idx + (size_t)a0 * pb, cnt * pb, ncclUint8, to, comm, xs));
       }
       if (runs[ph].len[from] > 0) {
         const size_t cnt = (size_t)(lead[ph][from] + runs[ph].len[from]);
         CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[ph][from] * kb, cnt * kb, ncclUint8, from, comm, xs));
-        if (argsort) CK_NCCL(ncclRecv(r_idx + recv_off[ph][from], cnt, ncclInt64, from, comm, xs));
+        if (argsort)
+          CK_NCCL(ncclRecv(r_idx + (size_t)recv_off[ph][from] * 8, cnt * pay_bytes[from], ncclUint8, from, comm, xs));
       }
     }
     CK_NCCL(ncclGroupEnd());
@@ -569,7 +609,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
       CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[ph][rank] * kb, k_bytes + (size_t)c0 * kb,
                               (size_t)(c1 - c0) * kb, cudaMemcpyDeviceToDevice, stream));
       if (argsort)
-        CK_CUDA(cudaMemcpyAsync(r_idx + recv_off[ph][rank], idx + c0, (size_t)(c1 - c0) * 8,
+        CK_CUDA(cudaMemcpyAsync(r_idx + (size_t)recv_off[ph][rank] * 8, idx + (size_t)c0 * pb, (size_t)(c1 - c0) * pb,
                                 cudaMemcpyDeviceToDevice, stream));
     }
     CK_CUDA(cudaStreamWaitEvent(stream, ev_done[ph], 0));

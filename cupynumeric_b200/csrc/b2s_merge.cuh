@@ -17,7 +17,9 @@ constexpr int MERGE_TILE     = MERGE_THREADS * MERGE_VT;
 
 struct MergeRuns {
   const void* keys[MERGE_MAX_RUNS];     // run i: len[i] sorted keys
-  const int64_t* idx[MERGE_MAX_RUNS];   // payload of run i (argsort) or null
+  const void* idx[MERGE_MAX_RUNS];      // payload of run i (argsort) or null
+  long long idx_base[MERGE_MAX_RUNS];   // added to a 32-bit payload
+  int idx_bytes[MERGE_MAX_RUNS];        // payload width of run i: 8 (int64) or 4 (uint32 + idx_base)
   long long len[MERGE_MAX_RUNS];
   int nruns;
 };
@@ -41,13 +43,38 @@ __device__ __forceinline__ long long lower_bound_okey(const void* base, long lon
   return lo;
 }
 
+// The same search with ARY - 1 probes per step.  The probes of a step are independent loads, so a
+// step costs one memory latency like a step of the binary search, and there are log2(ARY) times
+// fewer steps: the searches of the partition kernel are chains of dependent loads and nothing else.
+template <int KB, int ARY>
+__device__ __forceinline__ long long lower_bound_okey_wide(const void* base, long long lo, long long hi,
+                                                           unsigned long long x, int xf)
+{
+  static_assert(ARY >= 2 && (ARY & (ARY - 1)) == 0, "ARY must be a power of two");
+  constexpr int SH = ARY == 2 ? 1 : ARY == 4 ? 2 : ARY == 8 ? 3 : 4;
+  while (hi - lo >= ARY) {
+    const long long span = hi - lo;
+    int c = 0;  // probes with key < x; the keys are sorted, so these are the first c probes
+#pragma unroll
+    for (int j = 1; j < ARY; ++j) c += okey_at<KB>(base, lo + ((span * j) >> SH), xf) < x ? 1 : 0;
+    const long long nlo = c == 0 ? lo : lo + ((span * c) >> SH) + 1;
+    const long long nhi = c == ARY - 1 ? hi : lo + ((span * (c + 1)) >> SH);
+    lo = nlo;
+    hi = nhi;
+  }
+  int c = 0;
+#pragma unroll
+  for (int j = 0; j < ARY - 1; ++j) c += (lo + j < hi && okey_at<KB>(base, lo + j, xf) < x) ? 1 : 0;
+  return lo + c;
+}
+
 // cuts[b * nruns + i] = number of elements of run i among the first b * MERGE_TILE elements of
 // the stable merge; b = 0 .. ntiles.
 //
 // Two launches: the first handles every `stride`-th boundary (coarse == nullptr) and searches
 // the whole runs; the second handles all boundaries and searches only between the two coarse
 // cuts that enclose each one, where both the index range and the key range are narrow.
-template <int KB>
+template <int KB, int ARY>
 __global__ void __launch_bounds__(256)
 merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf, long long* __restrict__ cuts,
                        long long stride, int fine)
@@ -110,7 +137,7 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
   for (int bit = BITS - 1; bit >= 0; --bit) {
     const bool step               = search && bit <= top;
     const unsigned long long cand = x | (1ull << bit);
-    const long long p = step ? lower_bound_okey<KB>(base, lo, hi, cand, xf) : 0;
+    const long long p = step ? lower_bound_okey_wide<KB, ARY>(base, lo, hi, cand, xf) : 0;
     long long less    = p;
     for (int s = gw >> 1; s > 0; s >>= 1) less += __shfl_xor_sync(0xFFFFFFFFu, less, s);
     if (step) {
@@ -126,7 +153,7 @@ merge_partition_kernel(MergeRuns runs, long long total, long long ntiles, int xf
   const long long lower = lo;
   long long upper       = hi0;
   if (search && x != (BITS == 64 ? ~0ull : ((1ull << (BITS & 63)) - 1)))
-    upper = lower_bound_okey<KB>(base, lo, hi0, x + 1, xf);
+    upper = lower_bound_okey_wide<KB, ARY>(base, lo, hi0, x + 1, xf);
   long long less_total = lower;
   for (int s = gw >> 1; s > 0; s >>= 1) less_total += __shfl_xor_sync(0xFFFFFFFFu, less_total, s);
   const long long equal = upper - lower;
@@ -163,17 +190,23 @@ struct MergeSmem {
   // Comparing the words orders by key, then by slot, which is run order: the merge stays stable
   // and needs no separate slot arrays.
   static constexpr bool PACK  = SLOTS && KB <= 4;
+  // merge-buffer entry: 4 bytes for plain integer keys of at most 32 bits, else 8
+  static constexpr size_t WB       = (!SLOTS && KB <= 4) ? 4 : 8;
   static constexpr size_t OFF_RAW  = 0;
   static constexpr size_t OFF_OK0  = (RAW ? ((size_t)MERGE_TILE * KB + 15) / 16 * 16 : 0);
-  static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_PADDED * 8;
-  static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_PADDED * 8;
+  static constexpr size_t OFF_OK1  = OFF_OK0 + (size_t)MERGE_PADDED * WB;
+  static constexpr size_t OFF_SL0  = OFF_OK1 + (size_t)MERGE_PADDED * WB;
   static constexpr size_t OFF_SL1  = OFF_SL0 + ((SLOTS && !PACK) ? (size_t)MERGE_PADDED * 2 : 0);
   static constexpr size_t OFF_BND  = (OFF_SL1 + ((SLOTS && !PACK) ? (size_t)MERGE_PADDED * 2 : 0) + 15) / 16 * 16;
   static constexpr size_t OFF_SRC  = (OFF_BND + (MERGE_MAX_RUNS + 1) * 4 + 15) / 16 * 16;  // 8-byte entries
   static constexpr size_t OFF_KP   = OFF_SRC + MERGE_MAX_RUNS * 8;   // run key pointers
   static constexpr size_t OFF_IP   = OFF_KP + MERGE_MAX_RUNS * 8;    // run payload pointers
-  static constexpr size_t BYTES    = OFF_IP + MERGE_MAX_RUNS * 8;
+  static constexpr size_t OFF_IB   = OFF_IP + MERGE_MAX_RUNS * 8;    // payload bases (negative: int64 payload)
+  static constexpr size_t BYTES    = OFF_IB + MERGE_MAX_RUNS * 8;
 };
+
+template <size_t B> struct MergeWord { using type = unsigned long long; };
+template <> struct MergeWord<4> { using type = uint32_t; };
 
 // inverse of to_ordered for the integer orderings
 template <int KB>
@@ -197,14 +230,15 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   constexpr bool RAW   = S::RAW;
   extern __shared__ __align__(16) unsigned char smem[];
   K* raw                    = reinterpret_cast<K*>(smem + S::OFF_RAW);
-  unsigned long long* ok[2] = {reinterpret_cast<unsigned long long*>(smem + S::OFF_OK0),
-                               reinterpret_cast<unsigned long long*>(smem + S::OFF_OK1)};
+  using W                   = typename MergeWord<S::WB>::type;
+  W* ok[2]                  = {reinterpret_cast<W*>(smem + S::OFF_OK0), reinterpret_cast<W*>(smem + S::OFF_OK1)};
   unsigned short* sl[2]     = {reinterpret_cast<unsigned short*>(smem + S::OFF_SL0),
                                reinterpret_cast<unsigned short*>(smem + S::OFF_SL1)};
   int* bnd                  = reinterpret_cast<int*>(smem + S::OFF_BND);        // piece starts in the tile
   long long* src0           = reinterpret_cast<long long*>(smem + S::OFF_SRC);  // piece starts in the runs
   const K** kptr            = reinterpret_cast<const K**>(smem + S::OFF_KP);
-  const int64_t** iptr      = reinterpret_cast<const int64_t**>(smem + S::OFF_IP);
+  const void** iptr         = reinterpret_cast<const void**>(smem + S::OFF_IP);
+  long long* ibase          = reinterpret_cast<long long*>(smem + S::OFF_IB);
 
   const int tid        = threadIdx.x;
   const long long b    = blockIdx.x;
@@ -219,6 +253,8 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   if (tid < MERGE_MAX_RUNS) {
     kptr[tid] = tid < nruns ? static_cast<const K*>(runs.keys[tid]) : nullptr;
     iptr[tid] = tid < nruns ? runs.idx[tid] : nullptr;
+    // a 32-bit payload is a position below 2^32 plus a non-negative base; -1 marks int64 payloads
+    ibase[tid] = (tid < nruns && runs.idx_bytes[tid] == 4) ? runs.idx_base[tid] : -1;
   }
   if (tid == 0) {
     int off = 0;
@@ -240,7 +276,7 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
       const K k = kp[q - q0];
       if (RAW) raw[q] = k;
       const unsigned long long o = (unsigned long long)to_ordered_rt<KB>(k, xf);
-      ok[0][mpad(q)] = PACK ? ((o << 32) | (unsigned long long)q) : o;
+      ok[0][mpad(q)] = PACK ? (W)((o << 32) | (unsigned long long)q) : (W)o;
       if (SLOTS) sl[0][mpad(q)] = (unsigned short)q;
     }
   }
@@ -249,9 +285,9 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   // tree of pairwise stable merges; ties take from the lower run first
   int cur = 0;
   for (int g = 2; g <= p2; g <<= 1) {
-    const unsigned long long* ik = ok[cur];
-    const unsigned short* is     = sl[cur];
-    unsigned long long* okd      = ok[cur ^ 1];
+    const W* ik              = ok[cur];
+    const unsigned short* is = sl[cur];
+    W* okd                   = ok[cur ^ 1];
     unsigned short* sld          = sl[cur ^ 1];
     int q        = tid * MERGE_VT;
     const int q1 = min(q + MERGE_VT, count);
@@ -268,8 +304,8 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
         if (ik[mpad(s0 + m)] <= ik[mpad(mid + diag - 1 - m)]) lo = m + 1; else hi = m;
       }
       int ia = s0 + lo, ib = mid + diag - lo;  // absolute read positions in the two runs
-      constexpr unsigned long long INF = ~0ull;
-      unsigned long long ka = ia < mid ? ik[mpad(ia)] : INF, kb = ib < s1 ? ik[mpad(ib)] : INF;
+      constexpr W INF = (W)~(W)0;
+      W ka = ia < mid ? ik[mpad(ia)] : INF, kb = ib < s1 ? ik[mpad(ib)] : INF;
 #pragma unroll
       for (int j = 0; j < MERGE_VT; ++j) {
         if (q < end) {
@@ -282,7 +318,7 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
           ib += take_a ? 0 : 1;
           const int nxt              = take_a ? ia : ib;
           const bool live            = take_a ? (ia < mid) : (ib < s1);
-          const unsigned long long v = live ? ik[mpad(nxt)] : INF;
+          const W v                  = live ? ik[mpad(nxt)] : INF;
           ka = take_a ? v : ka;
           kb = take_a ? kb : v;
           ++q;
@@ -294,15 +330,21 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
   }
 
   const unsigned short* fs     = sl[cur];
-  const unsigned long long* fp = ok[cur];
+  const W* fp                  = ok[cur];
   auto slot_of = [&](int q) -> unsigned int { return PACK ? (unsigned int)(fp[mpad(q)] & 0xFFFFu) : (unsigned int)fs[mpad(q)]; };
   if (ARGS) {
     // the merge buffer that is no longer read becomes the payload staging area
     int64_t* pay = reinterpret_cast<int64_t*>(ok[cur ^ 1]);
     for (int i = 0; i < nruns; ++i) {
       const int q0 = bnd[i], q1 = bnd[i + 1];
-      const int64_t* ip = iptr[i] + src0[i];
-      for (int q = q0 + tid; q < q1; q += MERGE_THREADS) pay[q] = ip[q - q0];
+      const long long ib = ibase[i];
+      if (ib < 0) {
+        const int64_t* ip = static_cast<const int64_t*>(iptr[i]) + src0[i];
+        for (int q = q0 + tid; q < q1; q += MERGE_THREADS) pay[q] = ip[q - q0];
+      } else {
+        const uint32_t* ip = static_cast<const uint32_t*>(iptr[i]) + src0[i];
+        for (int q = q0 + tid; q < q1; q += MERGE_THREADS) pay[q] = (int64_t)ip[q - q0] + ib;
+      }
     }
     __syncthreads();
     int64_t* o = static_cast<int64_t*>(out) + base;
@@ -312,7 +354,7 @@ merge_tiles_kernel(MergeRuns runs, long long total, int xf, const long long* __r
     for (int q = tid; q < count; q += MERGE_THREADS) o[q] = raw[slot_of(q)];
   } else {
     K* o                         = static_cast<K*>(out) + base;
-    const unsigned long long* fk = ok[cur];
+    const W* fk                  = ok[cur];
     for (int q = tid; q < count; q += MERGE_THREADS) o[q] = from_ordered_int<KB>(fk[mpad(q)], xf);
   }
 }

@@ -89,6 +89,7 @@ struct RouteArgs {
   const void* keys_in;
   void* keys_out;     // may be null (argsort)
   int64_t* idx_out;   // may be null (sort)
+  uint32_t* idx_out32; // instead of idx_out: positions without offset, 32 bits wide
   void* tmp_keys[2];
   uint32_t* tmp_idx[2];
   unsigned int n;
@@ -137,6 +138,7 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
       if (last) {
         pd.dst_keys  = a.keys_out;
         pd.dst_idx64 = a.idx_out;
+        pd.dst_idx32 = a.idx_out32;
         if (a.keys_out != nullptr && a.keys_out == cur_keys) {
           // a single effective pass over an in-place call: go through a temporary
           pd.dst_keys    = a.tmp_keys[0];
@@ -146,7 +148,7 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
         }
       } else {
         pd.dst_keys = a.tmp_keys[j & 1];
-        pd.dst_idx32 = a.idx_out ? a.tmp_idx[j & 1] : nullptr;
+        pd.dst_idx32 = (a.idx_out || a.idx_out32) ? a.tmp_idx[j & 1] : nullptr;
       }
       cur_keys = pd.dst_keys;
       cur_idx  = pd.dst_idx32;
@@ -161,7 +163,8 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
       fix.copy_dst   = a.keys_out;
       fix.copy_bytes = (unsigned long long)a.n * a.key_bytes;
     }
-    fix.synth_idx = a.idx_out;
+    fix.synth_idx   = a.idx_out;
+    fix.synth_idx32 = a.idx_out32;
   }
   ctrl->fix = fix;
 }
@@ -239,6 +242,9 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
   }
   if (f.synth_idx != nullptr) {
     for (size_t i = gthread; i < n; i += gstride) f.synth_idx[i] = index_offset + (int64_t)i;
+  }
+  if (f.synth_idx32 != nullptr) {
+    for (size_t i = gthread; i < n; i += gstride) f.synth_idx32[i] = (uint32_t)i;
   }
 }
 
