@@ -76,6 +76,9 @@ def main():
         shard, argsort = w.c5_uint64_nearly_sorted_shard(n, rank, world), True
     elif workload == "tiny":
         shard, argsort = np.random.default_rng(rank).integers(-5, 5, 1000).astype(np.int32), True
+    elif workload == "mixed":   # a long tile (32-bit positions in the exchange) beside a short one (int64)
+        m = 50000 if rank == 0 else 700
+        shard, argsort = np.random.default_rng(7 + rank).integers(-40, 40, m).astype(np.int16), True
     elif workload == "empty":   # only rank 0 holds data; everybody still takes part
         shard = np.arange(5000, 0, -1, dtype=np.int64) if rank == 0 else np.empty(0, dtype=np.int64)
         argsort = False
@@ -102,7 +105,7 @@ def main():
         assert same, "distributed result differs from the global stable sort"
         assert starts == [int(x) for x in np.cumsum([0] + [len(p) for p in parts])[:-1]], starts
         sizes = [len(p) for p in parts]
-        if workload not in ("tiny", "empty"):
+        if workload not in ("tiny", "empty", "mixed"):
             assert max(sizes) <= 1.2 * sum(sizes) / world + 16, sizes
         print("DIST_OK", workload, sizes)
     destroy_comm()
