@@ -11,7 +11,7 @@ struct DtypeInfo {
   int xf;
 };
 
-// Key width and ordering rule per element type; complex types are not radix keys.
+// Key width and ordering rule per element type; complex128 is not a radix key (16 bytes).
 inline bool dtype_info(int dtype, DtypeInfo* o)
 {
   switch (dtype) {
@@ -27,6 +27,7 @@ inline bool dtype_info(int dtype, DtypeInfo* o)
     case B2S_FLOAT16: *o = {2, XF_FLOAT}; return true;
     case B2S_FLOAT32: *o = {4, XF_FLOAT}; return true;
     case B2S_FLOAT64: *o = {8, XF_FLOAT}; return true;
+    case B2S_COMPLEX64: *o = {8, XF_CFLOAT}; return true;  // (real, imaginary) as one 8-byte key
     default: return false;
   }
 }
@@ -188,7 +189,7 @@ int b2s_workspace_bytes(int dtype, size_t volume, size_t segment, int argsort, s
 {
   DtypeInfo di;
   if (bytes == nullptr) return B2S_ERR_INVALID_ARG;
-  if (dtype == B2S_COMPLEX64 || dtype == B2S_COMPLEX128) {
+  if (dtype == B2S_COMPLEX128) {
     if (volume > 0 && (segment == 0 || volume % segment != 0)) return B2S_ERR_INVALID_ARG;
     return complex_ws_bytes(dtype, volume, segment, bytes);
   }
@@ -220,7 +221,7 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
 {
   (void)stable;  // always stable
   DtypeInfo di;
-  if (dtype == B2S_COMPLEX64 || dtype == B2S_COMPLEX128) {
+  if (dtype == B2S_COMPLEX128) {
     if (ndim_is_1 && volume != segment) return B2S_ERR_INVALID_ARG;
     return complex_local_sort(dtype, keys_in, keys_out, idx_out, volume, segment, index_offset, ws, ws_bytes,
                               static_cast<cudaStream_t>(cuda_stream));

@@ -27,7 +27,8 @@ template <> struct KeyOf<8> { using type = uint64_t; };
 enum : int {
   XF_UNSIGNED = 0,  // bool, uintN
   XF_SIGNED   = 1,  // intN: flip the sign bit
-  XF_FLOAT    = 2   // IEEE floats: -inf < .. < -0.0 == +0.0 < .. < +inf < every NaN
+  XF_FLOAT    = 2,  // IEEE floats: -inf < .. < -0.0 == +0.0 < .. < +inf < every NaN
+  XF_CFLOAT   = 3   // complex64 as one 8-byte key: (real, imaginary) lexicographic, each part as XF_FLOAT
 };
 
 // Maps raw key bits to an unsigned integer whose natural order is the sort order.
@@ -44,6 +45,14 @@ __host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered(typename
     return raw;
   } else if (XF == XF_SIGNED) {
     return (K)(raw ^ SB);
+  } else if (XF == XF_CFLOAT) {
+    // the real part is the first float in memory (the low word); it is the major key.  NaN-last
+    // per part gives NumPy's complex order: a NaN real part after every number, and among equal
+    // real parts a NaN imaginary part last.
+    const unsigned long long r64 = (unsigned long long)raw;
+    const unsigned int re = to_ordered<4, XF_FLOAT>((unsigned int)r64);
+    const unsigned int im = to_ordered<4, XF_FLOAT>((unsigned int)(r64 >> 32));
+    return (K)(((unsigned long long)re << 32) | im);
   } else {
     // exponent mask: all exponent bits set = inf/NaN
     constexpr K EXP = (KB == 2) ? (K)0x7C00u : (KB == 4) ? (K)0x7F800000u : (K)0x7FF0000000000000ull;
@@ -80,6 +89,7 @@ __host__ __device__ __forceinline__ typename KeyOf<KB>::type to_ordered_rt(typen
 {
   if (xf == XF_UNSIGNED) return to_ordered<KB, XF_UNSIGNED>(raw);
   if (xf == XF_SIGNED) return to_ordered<KB, XF_SIGNED>(raw);
+  if (KB == 8 && xf == XF_CFLOAT) return to_ordered<(KB == 8 ? 8 : 4), (KB == 8 ? (int)XF_CFLOAT : (int)XF_UNSIGNED)>(raw);
   if (KB >= 2) return to_ordered<(KB >= 2 ? KB : 2), XF_FLOAT>(raw);
   return raw;
 }
@@ -285,6 +295,11 @@ __device__ __forceinline__ unsigned int digit_fast(typename KeyOf<KB>::type raw,
 {
   if (XF == XF_FLOAT) {
     return (unsigned int)(to_ordered<KB, XF>(raw) >> shift) & (RADIX - 1);
+  } else if (XF == XF_CFLOAT) {
+    // passes 0-3 look at the imaginary part (high word in memory), passes 4-7 at the real part
+    const unsigned long long r64 = (unsigned long long)raw;
+    const unsigned int w         = s.hi_word ? (unsigned int)r64 : (unsigned int)(r64 >> 32);
+    return (to_ordered<4, XF_FLOAT>(w) >> (shift & 31)) & (RADIX - 1);
   } else if (KB == 8) {
     const unsigned long long r64 = (unsigned long long)raw;
     const unsigned int w         = s.hi_word ? (unsigned int)(r64 >> 32) : (unsigned int)r64;

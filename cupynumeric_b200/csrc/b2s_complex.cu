@@ -1,4 +1,5 @@
-// Complex keys: lexicographic (real, imaginary) order, the order the reference's Thrust path
+// complex128 keys (complex64 is an 8-byte radix key of its own, XF_CFLOAT, and does not come
+// here): lexicographic (real, imaginary) order, the order the reference's Thrust path
 // uses for complex64/128 (src/cupynumeric/sort/thrust_sort.cuh:61-123 with the comparison of
 // src/cupynumeric/binary/binary_op_util.h:32-36).  Done as two stable radix argsorts - by the
 // imaginary parts, then by the real parts in that order - which is the lexicographic order.

@@ -43,6 +43,7 @@ static int kb_of(int dtype, int* xf)
     case B2S_INT64: *xf = XF_SIGNED; return 8;
     case B2S_UINT64: *xf = XF_UNSIGNED; return 8;
     case B2S_FLOAT64: *xf = XF_FLOAT; return 8;
+    case B2S_COMPLEX64: *xf = XF_CFLOAT; return 8;
     default: return 0;
   }
 }
@@ -177,7 +178,7 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
       kern<<<(unsigned int)ntiles, MERGE_THREADS, bytes, stream>>>(runs, total, xf, d_tcuts, out);
       return cudaSuccess;
     };
-    const bool flt = xf == XF_FLOAT;
+    const bool flt = xf == XF_FLOAT || xf == XF_CFLOAT;  // ordered image cannot be mapped back
     cudaError_t ee;
     if (args && flt) ee = launch(merge_tiles_kernel<KB, true, true>, MergeSmem<KB, true, true>::BYTES);
     else if (args) ee = launch(merge_tiles_kernel<KB, true, false>, MergeSmem<KB, true, false>::BYTES);
@@ -227,6 +228,22 @@ struct PhaseTrace {
     t0 = t1;
   }
   ~PhaseTrace() { if (on) std::fprintf(stderr, "[b2s dist ms r%d]%s\n", rk, line); }
+};
+
+// CUDA events that are destroyed on every way out of the function that owns them
+struct Events {
+  std::vector<cudaEvent_t> ev;
+  cudaEvent_t make()
+  {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    ev.push_back(e);
+    return e;
+  }
+  ~Events()
+  {
+    for (cudaEvent_t e : ev) cudaEventDestroy(e);
+  }
 };
 
 #define CK_CUDA(x) do { if ((x) != cudaSuccess) return B2S_ERR_CUDA; } while (0)
@@ -568,10 +585,13 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   // The exchange runs on a stream of its own so that it overlaps the merges on the caller's.
   cudaStream_t xs = exchange_stream();
   if (xs == nullptr) return B2S_ERR_CUDA;
-  cudaEvent_t ev_ready = nullptr;
+  Events events;
+  cudaEvent_t ev_ready = events.make();
   std::vector<cudaEvent_t> ev_done(nph, nullptr);
-  CK_CUDA(cudaEventCreateWithFlags(&ev_ready, cudaEventDisableTiming));
-  for (auto& e : ev_done) CK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  for (auto& e : ev_done) e = events.make();
+  if (ev_ready == nullptr) return B2S_ERR_CUDA;
+  for (auto e : ev_done)
+    if (e == nullptr) return B2S_ERR_CUDA;
   CK_CUDA(cudaEventRecord(ev_ready, stream));
   CK_CUDA(cudaStreamWaitEvent(xs, ev_ready, 0));
   for (int ph = 0; ph < nph; ++ph) {
@@ -625,8 +645,6 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   CK_CUDA(cudaStreamSynchronize(stream));
   CK_CUDA(cudaStreamSynchronize(xs));
   trace.mark("exchange+merge(sync)");
-  cudaEventDestroy(ev_ready);
-  for (auto& e : ev_done) cudaEventDestroy(e);
   mem.disown(result);
   *out_ptr = result;
   *out_len = (size_t)total;

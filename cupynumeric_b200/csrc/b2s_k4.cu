@@ -1,5 +1,5 @@
 // Kernels of the local sort for 4-byte keys.
 #include "b2s_launch.cuh"
 namespace b2s {
-B2S_INSTANTIATE_KEY_WIDTH(4, true)
+B2S_INSTANTIATE_KEY_WIDTH(4, true, false)
 }

@@ -289,7 +289,7 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
   return segsort_cfg<KB, PAIRS, 512, 16>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
 }
 
-#define B2S_INSTANTIATE_KEY_WIDTH(KB, HAS_FLOAT)                                                          \
+#define B2S_INSTANTIATE_KEY_WIDTH(KB, HAS_FLOAT, HAS_CFLOAT)                                                          \
   template <>                                                                                             \
   cudaError_t launch_radix_1d<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,    \
                                   int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32) \
@@ -298,6 +298,8 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
     if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
     if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
       return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
+    if (HAS_CFLOAT && xf == XF_CFLOAT)                                                                    \
+      return radix_1d_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
     return cudaErrorInvalidValue;                                                                         \
   }                                                                                                       \
   template <>                                                                                             \
@@ -309,6 +311,8 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
     if (xf == XF_SIGNED) return radix_seg_xf<KB, XF_SIGNED>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
     if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
       return radix_seg_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
+    if (HAS_CFLOAT && xf == XF_CFLOAT)                                                                    \
+      return radix_seg_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, seg_len, nseg, index_offset, ws, stream); \
     return cudaErrorInvalidValue;                                                                         \
   }                                                                                                       \
   template <>                                                                                             \
@@ -316,7 +320,7 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
                                  unsigned long long nseg, int64_t index_offset, Ctrl* ctrl,               \
                                  cudaStream_t stream)                                                     \
   {                                                                                                       \
-    if (!HAS_FLOAT && xf == XF_FLOAT) return cudaErrorInvalidValue;                                       \
+    if ((!HAS_FLOAT && xf == XF_FLOAT) || (!HAS_CFLOAT && xf == XF_CFLOAT)) return cudaErrorInvalidValue; \
     if (idx_out != nullptr)                                                                               \
       return segsort_pairs<KB, true>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);    \
     return segsort_pairs<KB, false>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);     \

@@ -55,6 +55,7 @@ extern "C" int b2s_searchsorted(int dtype, const void* sorted_tile, size_t n_til
     case B2S_UINT64: kb = 8; xf = XF_UNSIGNED; break;
     case B2S_INT64: kb = 8; xf = XF_SIGNED; break;
     case B2S_FLOAT64: kb = 8; xf = XF_FLOAT; break;
+    case B2S_COMPLEX64: kb = 8; xf = XF_CFLOAT; break;
     default: return B2S_ERR_UNSUPPORTED;
   }
   if (num_values == 0) return B2S_OK;

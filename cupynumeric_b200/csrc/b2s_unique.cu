@@ -157,6 +157,7 @@ int b2s_unique_sorted(int dtype, const void* sorted, size_t n, void* out, size_t
     case B2S_UINT64: kb = 8; xf = XF_UNSIGNED; break;
     case B2S_INT64: kb = 8; xf = XF_SIGNED; break;
     case B2S_FLOAT64: kb = 8; xf = XF_FLOAT; break;
+    case B2S_COMPLEX64: kb = 8; xf = XF_CFLOAT; break;
     default: return B2S_ERR_UNSUPPORTED;
   }
   if (out_len == nullptr) return B2S_ERR_INVALID_ARG;

@@ -21,7 +21,7 @@ KINDS = ["hist", "scan", "sweep", "fixup", "segsort", "unit", "dist", "merge", "
 
 
 def _random(dtype: torch.dtype, n: int) -> torch.Tensor:
-    if dtype.is_floating_point:
+    if dtype.is_floating_point or dtype.is_complex:
         return torch.randn(n, device="cuda", dtype=dtype)
     info = torch.iinfo(dtype)
     return torch.randint(max(info.min, -2**62), min(info.max, 2**62), (n,), device="cuda", dtype=torch.int64).to(dtype)

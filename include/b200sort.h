@@ -20,7 +20,8 @@
  *   - the sort is always stable, whatever `stable` says (the reference's radix
  *     path ignores the flag too, src/cupynumeric/sort/sort.cu:63-81); floats sort
  *     as -inf < ... < -0.0 == +0.0 < ... < +inf < NaN with the input's bit
- *     patterns preserved; complex keys sort by (real, imaginary).
+ *     patterns preserved; complex keys sort by (real, imaginary), each part
+ *     ordered like a float (complex64 keys must be 8-byte aligned).
  */
 #ifndef B200SORT_H_
 #define B200SORT_H_

@@ -79,6 +79,10 @@ def main():
     elif workload == "mixed":   # a long tile (32-bit positions in the exchange) beside a short one (int64)
         m = 50000 if rank == 0 else 700
         shard, argsort = np.random.default_rng(7 + rank).integers(-40, 40, m).astype(np.int16), True
+    elif workload == "c64":     # complex64 keys: one 8-byte (real, imaginary) radix key
+        rng = np.random.default_rng(31 + rank)
+        shard = (rng.integers(-30, 30, 60_000) + 1j * rng.integers(-30, 30, 60_000)).astype(np.complex64)
+        argsort = True
     elif workload == "empty":   # only rank 0 holds data; everybody still takes part
         shard = np.arange(5000, 0, -1, dtype=np.int64) if rank == 0 else np.empty(0, dtype=np.int64)
         argsort = False

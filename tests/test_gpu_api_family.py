@@ -67,6 +67,8 @@ def test_unique(cuda_device):
             got = num.unique(a).to_numpy()
             want = np.unique(a)
             assert got.shape == want.shape and np.array_equal(got, want, equal_nan=np.dtype(dtype).kind == "f"), (dtype, n)
+    c = (rng.integers(-6, 6, 50_000) + 1j * rng.integers(-6, 6, 50_000)).astype(np.complex64)
+    assert np.array_equal(num.unique(c).to_numpy(), np.unique(c))        # complex64: one 8-byte key
     m = rng.integers(0, 10, (30, 40)).astype(np.int32)
     assert np.array_equal(num.unique(m).to_numpy(), np.unique(m))
     with pytest.raises(NotImplementedError):

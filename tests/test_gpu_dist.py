@@ -91,7 +91,7 @@ def test_dist_entry_point_single_rank(cuda_device):
         assert np.array_equal(res, want)
 
 
-@pytest.mark.parametrize("workload", ["c4", "c5", "f32", "tiny", "mixed", "empty", "split2d", "search"])
+@pytest.mark.parametrize("workload", ["c4", "c5", "f32", "tiny", "mixed", "c64", "empty", "split2d", "search"])
 def test_two_rank_sort_over_nccl(cuda_device, workload):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -26,6 +26,14 @@ def test_searchsorted_matches_numpy(cuda_device, dtype, side):
         assert np.array_equal(got, np.searchsorted(a, v, side=side)), (np.dtype(dtype), side, n)
 
 
+def test_searchsorted_complex64(cuda_device):
+    rng = np.random.default_rng(5)
+    a = np.sort((rng.integers(-9, 9, 20_000) + 1j * rng.integers(-9, 9, 20_000)).astype(np.complex64))
+    v = (rng.integers(-11, 11, 3000) + 1j * rng.integers(-11, 11, 3000)).astype(np.complex64)
+    for side in ("left", "right"):
+        assert np.array_equal(num.searchsorted(a, v, side=side).to_numpy(), np.searchsorted(a, v, side=side))
+
+
 def test_searchsorted_shapes_promotion_sorter_and_errors(cuda_device):
     rng = np.random.default_rng(4)
     a = np.sort(rng.standard_normal(5000).astype(np.float32))
