@@ -15,6 +15,7 @@
 
 #include "../../include/b200sort.h"
 #include "b2s_common.cuh"
+#include "b2s_peer.cuh"
 
 namespace b2s {
 // defined with the local sort
@@ -74,7 +75,7 @@ __global__ void sample_kernel(const void* sorted, long long n, int s, int rank, 
 // cuts[k] for k = 1..nranks-1: how many of my sorted elements go to ranks < k.
 template <int KB>
 __global__ void cut_kernel(const void* sorted, long long n, const Sample* splitters, int nranks, int rank,
-                           int xf, long long* cuts, long long tag0, long long tag1)
+                           int xf, long long* cuts, long long tag0, long long tag1, long long tag2)
 {
   const int k = blockIdx.x * blockDim.x + threadIdx.x + 1;
   if (k >= nranks) return;
@@ -91,8 +92,9 @@ __global__ void cut_kernel(const void* sorted, long long n, const Sample* splitt
   if (k == 1) {
     cuts[0]          = 0;
     cuts[nranks]     = n;
-    cuts[nranks + 1] = tag0;  // two words that travel with the cuts to every rank
+    cuts[nranks + 1] = tag0;  // three words that travel with the cuts to every rank
     cuts[nranks + 2] = tag1;
+    cuts[nranks + 3] = tag2;
   }
 }
 
@@ -436,8 +438,9 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   // the others which form it sends (payload width and offset travel with the cut positions).
   const bool pos32 = argsort && nranks > 1 && local_sort_pos32_supported(n_local);
   const size_t pb  = pos32 ? 4 : 8;  // bytes per payload element I send
-  void* keys       = mem.get((size_t)n * kb);
-  unsigned char* idx = argsort ? static_cast<unsigned char*>(mem.get((size_t)n * pb)) : nullptr;
+  // 16 spare bytes: the peer-memory exchange copies whole 16-byte vectors out of these buffers
+  void* keys       = mem.get((size_t)n * kb + 16);
+  unsigned char* idx = argsort ? static_cast<unsigned char*>(mem.get((size_t)n * pb + 16)) : nullptr;
   if (keys == nullptr || (argsort && idx == nullptr)) return B2S_ERR_WORKSPACE;
   void* sort_ws = nullptr;
   if (n > 0) {
@@ -476,25 +479,62 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   const int nph      = DIST_PHASES;  // the same on every rank by construction
   const int nb       = nranks * nph;  // buckets: bucket q goes to rank q / nph in phase q % nph
   const int s        = SAMPLES_PER_RANK;
-  Sample* d_samples  = static_cast<Sample*>(mem.get(sizeof(Sample) * s * nranks));
+  // every rank's block of the first all-gather: its samples, then what the others need to read
+  // its sorted buffers directly (PeerRecord)
+  const size_t blk      = sizeof(Sample) * s + sizeof(PeerRecord);
+  unsigned char* d_blk  = static_cast<unsigned char*>(mem.get(blk * nranks));
   Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nb));
-  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 3)));
-  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 3)));
-  if (!d_samples || !d_split || !d_cuts || !d_count) return B2S_ERR_WORKSPACE;
+  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 4)));
+  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 4)));
+  int* d_done        = static_cast<int*>(mem.get(256));
+  if (!d_blk || !d_split || !d_cuts || !d_count || !d_done) return B2S_ERR_WORKSPACE;
+  PeerRecord my_rec;
+  {
+    void* bufs[PEER_BUFFERS] = {keys, idx};
+    export_buffers(bufs, argsort ? 2 : 1, &my_rec);
+  }
   {
     prof::Scope ps(prof::K_DIST, stream);
     by_width(kb, [&](auto w) {
-      sample_kernel<decltype(w)::value><<<(s + 127) / 128, 128, 0, stream>>>(keys, n, s, rank, xf, d_samples + (size_t)rank * s);
+      sample_kernel<decltype(w)::value><<<(s + 127) / 128, 128, 0, stream>>>(
+        keys, n, s, rank, xf, reinterpret_cast<Sample*>(d_blk + (size_t)rank * blk));
       return cudaSuccess;
     });
   }
   CK_CUDA(cudaGetLastError());
+  CK_CUDA(cudaMemcpyAsync(d_blk + (size_t)rank * blk + sizeof(Sample) * s, &my_rec, sizeof(PeerRecord),
+                          cudaMemcpyHostToDevice, stream));
   if (barrier) barrier(barrier_ctx);
-  CK_NCCL(ncclAllGather(d_samples + (size_t)rank * s, d_samples, sizeof(Sample) * s, ncclUint8, comm, stream));
+  CK_NCCL(ncclAllGather(d_blk + (size_t)rank * blk, d_blk, blk, ncclUint8, comm, stream));
   if (barrier) barrier(barrier_ctx);
+  std::vector<unsigned char> h_blk(blk * nranks);
   std::vector<Sample> h_samples((size_t)s * nranks), h_split(nb);
-  CK_CUDA(cudaMemcpyAsync(h_samples.data(), d_samples, sizeof(Sample) * s * nranks, cudaMemcpyDeviceToHost, stream));
+  CK_CUDA(cudaMemcpyAsync(h_blk.data(), d_blk, blk * nranks, cudaMemcpyDeviceToHost, stream));
   CK_CUDA(cudaStreamSynchronize(stream));
+  std::vector<PeerRecord> recs(nranks);
+  for (int p = 0; p < nranks; ++p) {
+    std::memcpy(&h_samples[(size_t)p * s], &h_blk[(size_t)p * blk], sizeof(Sample) * s);
+    std::memcpy(&recs[p], &h_blk[(size_t)p * blk + sizeof(Sample) * s], sizeof(PeerRecord));
+  }
+  // Can I read everybody's buffers?  All ranks see the same records, so they agree on the first
+  // part; whether the mappings open is local and travels with the cut positions below.
+  std::vector<const unsigned char*> peer_keys(nranks, nullptr), peer_idx(nranks, nullptr);
+  long long can_pull = 1;
+  for (int p = 0; p < nranks && can_pull; ++p) {
+    if (!recs[p].ok || recs[p].nbuf != (unsigned long long)(argsort ? 2 : 1)) can_pull = 0;
+    if (p != rank && recs[p].pid == my_rec.pid) can_pull = 0;
+  }
+  for (int p = 0; p < nranks && can_pull; ++p) {
+    if (p == rank) continue;
+    const unsigned char* kbase = static_cast<const unsigned char*>(open_peer_allocation(recs[p].handle[0]));
+    const unsigned char* ibase = argsort ? static_cast<const unsigned char*>(open_peer_allocation(recs[p].handle[1])) : nullptr;
+    if (kbase == nullptr || (argsort && ibase == nullptr)) {
+      can_pull = 0;
+      break;
+    }
+    peer_keys[p] = kbase + recs[p].off[0];
+    peer_idx[p]  = argsort ? ibase + recs[p].off[1] : nullptr;
+  }
   trace.mark("local_sort+samples(sync)");
   if (sort_ws != nullptr) {
     // a wait inside the local sort that ran out shows up here; every rank still goes on to the
@@ -510,12 +550,12 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     prof::Scope ps(prof::K_DIST, stream);
     by_width(kb, [&](auto w) {
       cut_kernel<decltype(w)::value><<<(nb + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nb, rank, xf, d_cuts,
-                                                                        (long long)pb, (long long)global_offset);
+                                                                        (long long)pb, (long long)global_offset, can_pull);
       return cudaSuccess;
     });
   }
   CK_CUDA(cudaGetLastError());
-  const size_t row = (size_t)nb + 3;  // nb + 1 cut positions, payload width, global offset
+  const size_t row = (size_t)nb + 4;  // nb + 1 cut positions, payload width, global offset, can-pull flag
   std::vector<long long> h_allcuts((size_t)nranks * row);
   if (barrier) barrier(barrier_ctx);
   CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * row, ncclUint8, comm, stream));
@@ -526,6 +566,8 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   for (int src = 0; src < nranks; ++src)
     for (int q = 0; q < nb; ++q)
       if (h_allcuts[src * row + q] > h_allcuts[src * row + q + 1]) return B2S_ERR_INVALID_ARG;  // protocol mismatch
+  bool use_pull = true;  // the same on every rank: everybody sees everybody's flag
+  for (int src = 0; src < nranks; ++src) use_pull = use_pull && h_allcuts[src * row + nb + 3] == 1;
   std::vector<size_t> pay_bytes(nranks);
   for (int src = 0; src < nranks; ++src) {
     const long long w = h_allcuts[src * row + nb + 1];
@@ -594,7 +636,52 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     if (e == nullptr) return B2S_ERR_CUDA;
   CK_CUDA(cudaEventRecord(ev_ready, stream));
   CK_CUDA(cudaStreamWaitEvent(xs, ev_ready, 0));
-  for (int ph = 0; ph < nph; ++ph) {
+  for (int ph = 0; ph < nph && use_pull; ++ph) {
+    // One kernel copies this phase's slices out of the other ranks' sorted buffers.  Their
+    // contents are final: the all-gather of the cut positions above completed after every
+    // rank's local sort in stream order.
+    PullPlan plan{};
+    for (int i = 1; i < nranks; ++i) {
+      const int from = (rank + i) % nranks;
+      if (runs[ph].len[from] <= 0) continue;
+      const long long start = h_allcuts[from * row + (size_t)rank * nph + ph];  // their slice for me
+      const long long a0    = start - lead[ph][from];
+      const size_t cnt      = (size_t)(lead[ph][from] + runs[ph].len[from]);
+      plan.src[plan.nseg]   = reinterpret_cast<const uint4*>(peer_keys[from] + (size_t)a0 * kb);
+      plan.dst[plan.nseg]   = reinterpret_cast<uint4*>(r_keys + (size_t)recv_off[ph][from] * kb);
+      plan.nvec[plan.nseg]  = (cnt * kb + 15) / 16;
+      ++plan.nseg;
+      if (argsort) {
+        plan.src[plan.nseg]  = reinterpret_cast<const uint4*>(peer_idx[from] + (size_t)a0 * pay_bytes[from]);
+        plan.dst[plan.nseg]  = reinterpret_cast<uint4*>(r_idx + (size_t)recv_off[ph][from] * 8);
+        plan.nvec[plan.nseg] = (cnt * pay_bytes[from] + 15) / 16;
+        ++plan.nseg;
+      }
+    }
+    if (plan.nseg > 0) {
+      for (int i = 0; i < plan.nseg; ++i)
+        if (((reinterpret_cast<uintptr_t>(plan.src[i]) | reinterpret_cast<uintptr_t>(plan.dst[i])) & 15u) != 0)
+          return B2S_ERR_INVALID_ARG;  // cannot happen with 256-byte aligned buffers and 32-element starts
+      int dev = 0, sms = 148;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      plan.ctas_per_seg = (2 * sms + plan.nseg - 1) / plan.nseg;
+      prof::begin(prof::K_XCHG, xs);
+      pull_kernel<<<(unsigned int)(plan.nseg * plan.ctas_per_seg), PULL_THREADS, 0, xs>>>(plan);
+      prof::end(prof::K_XCHG, xs);
+      CK_CUDA(cudaGetLastError());
+    }
+    CK_CUDA(cudaEventRecord(ev_done[ph], xs));
+  }
+  if (use_pull) {
+    // nobody may release or reuse its sorted buffers before every rank has finished reading
+    // them: a collective behind the copy kernels, which the final synchronisation waits for
+    CK_CUDA(cudaMemsetAsync(d_done, 0, sizeof(int), xs));
+    if (barrier) barrier(barrier_ctx);
+    CK_NCCL(ncclAllReduce(d_done, d_done, 1, ncclInt32, ncclSum, comm, xs));
+    if (barrier) barrier(barrier_ctx);
+  }
+  for (int ph = 0; ph < nph && !use_pull; ++ph) {
     if (barrier) barrier(barrier_ctx);
     prof::begin(prof::K_XCHG, xs);
     CK_NCCL(ncclGroupStart());
