@@ -93,9 +93,19 @@ def test_dist_entry_point_single_rank(cuda_device):
 
 @pytest.mark.parametrize("workload", ["c4", "c5", "f32", "tiny", "mixed", "c64", "empty", "split2d", "search"])
 def test_two_rank_sort_over_nccl(cuda_device, workload):
+    _two_rank(workload, {})
+
+
+@pytest.mark.parametrize("workload", ["f32", "mixed", "c4"])
+def test_two_rank_sort_nccl_exchange(cuda_device, workload):
+    """The same sort with the peer-memory exchange switched off: ncclSend/ncclRecv move the slices."""
+    _two_rank(workload, {"B2S_DIST_P2P": "0"})
+
+
+def _two_rank(workload, extra_env):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29731", os.path.join(ROOT, "tests", "dist_worker.py"), workload]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
