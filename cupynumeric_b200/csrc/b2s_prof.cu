@@ -65,6 +65,13 @@ extern "C" {
 int b2s_profile_enable(int on)
 {
   recycle();
+  // events are created here, not between the kernels that are being timed
+  constexpr size_t RESERVE = 4096;
+  while (on != 0 && g_pool.size() < RESERVE) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) break;
+    g_pool.push_back(e);
+  }
   g_enabled = on != 0;
   return B2S_OK;
 }
