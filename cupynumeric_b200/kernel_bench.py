@@ -3,8 +3,14 @@
     python -m cupynumeric_b200.kernel_bench merge --dtype int64 --runs 8 --log2 27 [--payload]
     python -m cupynumeric_b200.kernel_bench sort  --dtype float32 --log2 28 [--argsort] [--segment L]
 
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m cupynumeric_b200.kernel_bench dist --dtype float32 --log2 27 [--argsort]
+
 `merge` times b2s_kway_merge on `runs` sorted runs holding 2^log2 elements in all; `sort` times
-b2s_local_sort.  Small cases of these commands are what the ncu summaries under profiles/ capture.
+b2s_local_sort; `dist` (one process per GPU) times the distributed 1-D sort of 2^log2 keys per GPU,
+first without the per-kernel events (the step time), then with them (where the time goes).
+B2S_DIST_P2P=0 selects the NCCL exchange.  Small cases of these commands are what the ncu summaries
+under profiles/ capture.
 """
 from __future__ import annotations
 
@@ -92,6 +98,52 @@ def bench_sort(args) -> None:
     lib.b2s_profile_enable(0)
 
 
+def bench_dist(args) -> None:
+    import os
+    import time
+
+    import torch.distributed as dist
+
+    from . import array, argsort, sort
+    from ._dist import destroy_comm
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    lib = _lib.lib()
+    dtype = getattr(torch, args.dtype)
+    n = 1 << args.log2
+    torch.manual_seed(1000 + rank)
+    arr = array(_random(dtype, n), global_lo=rank * n)
+
+    def call():
+        return argsort(arr, kind="stable") if args.argsort else sort(arr)
+
+    def timed(profile: bool) -> float:
+        for _ in range(args.warmup):
+            call()
+        torch.cuda.synchronize()
+        dist.barrier()
+        lib.b2s_profile_enable(1 if profile else 0)
+        t0 = time.perf_counter()
+        for _ in range(args.iters):
+            call()          # returns after its own final synchronisation
+        torch.cuda.synchronize()
+        dist.barrier()
+        dt = torch.tensor([(time.perf_counter() - t0) / args.iters * 1e3], device="cuda", dtype=torch.float64)
+        dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return float(dt.item())
+
+    ms = timed(False)
+    timed(True)
+    parts = _report(lib, args.iters)
+    lib.b2s_profile_enable(0)
+    if rank == 0:
+        print(f"dist {args.dtype} 2^{args.log2}/GPU x{world} argsort={args.argsort}: {ms:.2f} ms/step -> "
+              f"{n * world / ms / 1e6:.1f} Gkeys/s; rank 0 kernels: {parts}")
+    destroy_comm()
+    dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -105,10 +157,20 @@ def main() -> None:
     s.add_argument("--log2", type=int, default=28)
     s.add_argument("--argsort", action="store_true")
     s.add_argument("--segment", type=int, default=0)
-    for p in (m, s):
+    d = sub.add_parser("dist")
+    d.add_argument("--dtype", default="float32")
+    d.add_argument("--log2", type=int, default=27)
+    d.add_argument("--argsort", action="store_true")
+    for p in (m, s, d):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
+    if args.what == "dist":
+        import os
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        bench_dist(args)
+        return
     torch.cuda.set_device(0)
     (bench_merge if args.what == "merge" else bench_sort)(args)
 
