@@ -519,6 +519,7 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   // Can I read everybody's buffers?  All ranks see the same records, so they agree on the first
   // part; whether the mappings open is local and travels with the cut positions below.
   std::vector<const unsigned char*> peer_keys(nranks, nullptr), peer_idx(nranks, nullptr);
+  PeerPins pins;  // declared after `mem` and before any kernel that reads a peer is launched
   long long can_pull = 1;
   for (int p = 0; p < nranks && can_pull; ++p) {
     if (!recs[p].ok || recs[p].nbuf != (unsigned long long)(argsort ? 2 : 1)) can_pull = 0;
@@ -526,8 +527,8 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
   }
   for (int p = 0; p < nranks && can_pull; ++p) {
     if (p == rank) continue;
-    const unsigned char* kbase = static_cast<const unsigned char*>(open_peer_allocation(recs[p].handle[0]));
-    const unsigned char* ibase = argsort ? static_cast<const unsigned char*>(open_peer_allocation(recs[p].handle[1])) : nullptr;
+    const unsigned char* kbase = static_cast<const unsigned char*>(pins.acquire(recs[p].handle[0]));
+    const unsigned char* ibase = argsort ? static_cast<const unsigned char*>(pins.acquire(recs[p].handle[1])) : nullptr;
     if (kbase == nullptr || (argsort && ibase == nullptr)) {
       can_pull = 0;
       break;

@@ -17,6 +17,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <vector>
 
 namespace b2s {
 
@@ -77,27 +78,92 @@ inline void export_buffers(void* const* bufs, int nbuf, PeerRecord* rec)
   rec->ok = 1;
 }
 
-// Mappings of other processes' allocations, opened once and kept (opening costs far more than
-// a sort; allocators hand out the same blocks again and again).
-inline void* open_peer_allocation(const cudaIpcMemHandle_t& h)
-{
-  static std::mutex mu;
-  static std::map<std::string, void*> cache;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::string key(reinterpret_cast<const char*>(&h), sizeof(h));
-  key.push_back((char)dev);
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) return it->second;
-  void* p = nullptr;
-  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
-    cudaGetLastError();
-    return nullptr;
+// Mappings of other processes' allocations, opened once and kept: opening costs far more than a
+// sort, and allocators hand out the same blocks again and again.  A mapping keeps the other
+// process's memory alive after it frees it, so the table is bounded (B2S_PEER_CACHE entries,
+// 256 by default): when it is full, the mapping that has gone unused the longest and that no
+// sort in flight holds is closed.
+class PeerMappings {
+ public:
+  // Maps the allocation behind `h` (or finds it) and pins it until release(); null on failure.
+  void* acquire(const cudaIpcMemHandle_t& h, std::string* key_out)
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::string key(reinterpret_cast<const char*>(&h), sizeof(h));
+    key.push_back((char)dev);
+    std::lock_guard<std::mutex> lock(mu_);
+    ++clock_;
+    auto it = table_.find(key);
+    if (it == table_.end()) {
+      if (table_.size() >= capacity()) evict_one();
+      void* p = nullptr;
+      if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+      }
+      it = table_.emplace(key, Entry{p, 0, 0}).first;
+    }
+    ++it->second.users;
+    it->second.last_used = clock_;
+    *key_out             = key;
+    return it->second.base;
   }
-  cache.emplace(std::move(key), p);
-  return p;
-}
+  void release(const std::string& key)
+  {
+    std::lock_guard<std::mutex> lock(mu_);
+    auto it = table_.find(key);
+    if (it != table_.end() && it->second.users > 0) --it->second.users;
+  }
+  static PeerMappings& instance()
+  {
+    static PeerMappings m;
+    return m;
+  }
+
+ private:
+  struct Entry {
+    void* base;
+    int users;                     // sorts in flight that read through this mapping
+    unsigned long long last_used;
+  };
+  static size_t capacity()
+  {
+    const char* e = std::getenv("B2S_PEER_CACHE");
+    const long v  = e ? std::atol(e) : 256;
+    return v < 1 ? 1 : (size_t)v;
+  }
+  void evict_one()
+  {
+    auto victim = table_.end();
+    for (auto it = table_.begin(); it != table_.end(); ++it)
+      if (it->second.users == 0 && (victim == table_.end() || it->second.last_used < victim->second.last_used))
+        victim = it;
+    if (victim == table_.end()) return;  // everything is in use: grow past the bound for now
+    cudaIpcCloseMemHandle(victim->second.base);
+    table_.erase(victim);
+  }
+  std::mutex mu_;
+  std::map<std::string, Entry> table_;
+  unsigned long long clock_ = 0;
+};
+
+// The mappings one sort holds, unpinned when the sort returns: by then its copy kernels have
+// finished, because the sort synchronises its streams before it returns.
+struct PeerPins {
+  std::vector<std::string> keys;
+  void* acquire(const cudaIpcMemHandle_t& h)
+  {
+    std::string k;
+    void* p = PeerMappings::instance().acquire(h, &k);
+    if (p != nullptr) keys.push_back(std::move(k));
+    return p;
+  }
+  ~PeerPins()
+  {
+    for (const auto& k : keys) PeerMappings::instance().release(k);
+  }
+};
 
 // ---- the copy kernel ----
 constexpr int PULL_MAX_SEGS = 64;   // (MERGE_MAX_RUNS - 1) sources x PEER_BUFFERS

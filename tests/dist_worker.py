@@ -21,6 +21,25 @@ def main():
     from cupynumeric_b200 import workloads as w
     from cupynumeric_b200._dist import destroy_comm
 
+    if workload == "recache":
+        # several sorts of growing size in one process with a one-entry mapping table
+        # (B2S_PEER_CACHE=1, set by the test): mappings of earlier calls get closed and replaced
+        keep = []
+        for m in (30_000, 400_000, 3_000_000, 30_000):
+            shard = np.random.default_rng(m + rank).integers(-1000, 1000, m).astype(np.int32)
+            shards = [None] * world
+            dist.all_gather_object(shards, shard)
+            res = num.argsort(num.array(shard, global_lo=rank * m), kind="stable")
+            keep.append(res)                       # holds its block, so later calls get other blocks
+            parts = [None] * world
+            dist.all_gather_object(parts, res.to_numpy())
+            assert np.array_equal(np.concatenate(parts), np.argsort(np.concatenate(shards), kind="stable")), m
+        dist.barrier()
+        if rank == 0:
+            print("DIST_OK recache")
+        destroy_comm()
+        dist.destroy_process_group()
+        return
     if workload == "search":
         # sort across the ranks, then look values up in the distributed result
         shard = np.random.default_rng(50 + rank).integers(-10_000, 10_000, 200_000).astype(np.int64)

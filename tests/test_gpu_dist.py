@@ -102,6 +102,11 @@ def test_two_rank_sort_nccl_exchange(cuda_device, workload):
     _two_rank(workload, {"B2S_DIST_P2P": "0"})
 
 
+def test_two_rank_peer_mapping_table_bound(cuda_device):
+    """Mappings of other ranks' allocations are closed and reopened when the table is full."""
+    _two_rank("recache", {"B2S_PEER_CACHE": "1"})
+
+
 def _two_rank(workload, extra_env):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
