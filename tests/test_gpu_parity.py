@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from oracle import np_argsort, np_sort, np_task_sort, thrust_task_sort
+from oracle import complex_lex_argsort, np_argsort, np_sort, np_task_sort, thrust_task_sort
 from tests.helpers import ALL_DTYPES, assert_bit_equal, cabi_local_sort, random_keys
 
 pytestmark = pytest.mark.gpu
@@ -188,20 +188,6 @@ def test_complex_lexicographic_order(cuda_device, dtype):
         assert np.array_equal(got_k, want_k)
 
 
-def _complex_lex_order(a, seg):
-    """Stable (real, imag) lexicographic argsort per segment with NaN last in each part and
-    -0.0 == +0.0: the order this library documents for complex keys whose parts hold NaNs (the
-    reference compares with raw '<', src/cupynumeric/binary/binary_op_util.h:32-36, which leaves
-    the place of NaNs open)."""
-    out = np.empty(a.size, dtype=np.int64)
-    for s0 in range(0, a.size, seg):
-        c = a[s0:s0 + seg]
-        re, im = c.real, c.imag
-        keys = (np.nan_to_num(im, nan=0.0), np.isnan(im), np.nan_to_num(re, nan=0.0), np.isnan(re))
-        out[s0:s0 + seg] = np.lexsort(keys)
-    return out
-
-
 @pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
 def test_complex_special_values(cuda_device, dtype):
     rng = np.random.default_rng(78)
@@ -209,7 +195,7 @@ def test_complex_special_values(cuda_device, dtype):
     for n, seg in ((4000, 4000), (50_000, 50_000), (40 * 500, 500), (3 * 10_000, 10_000)):
         a = (rng.choice(pool, n) + 1j * rng.choice(pool, n)).astype(dtype)
         a.real[rng.integers(0, n, n // 7)] = -0.0     # signed zeros in both parts
-        order = _complex_lex_order(a, seg)
+        order = complex_lex_argsort(a, seg)
         want_k = a.reshape(-1, seg)[np.arange(n // seg)[:, None], order.reshape(-1, seg)].reshape(-1)
         got_k, got_i = cabi_local_sort(a, seg, True, index_offset=0, ndim_is_1=seg == n, want_keys_too=True)
         assert np.array_equal(got_i, order), (n, seg)

@@ -7,7 +7,7 @@ import os
 import numpy as np
 import pytest
 
-from oracle import np_argsort, np_sort, np_task_sort, thrust_task_sort
+from oracle import complex_lex_argsort, np_argsort, np_sort, np_task_sort, thrust_task_sort
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 SORT = json.load(open(os.path.join(GOLDEN, "sort_cc.json")))
@@ -125,3 +125,17 @@ def test_index_rules():
     assert idx.tolist() == [101, 102, 100, 105, 104, 103]
     _, idx = thrust_task_sort(a, 3, True, index_offset=10, ndim_is_1=False)
     assert idx.tolist() == [11, 12, 10, 12, 11, 10]
+
+
+@pytest.mark.parametrize("dtype", [np.complex64, np.complex128])
+def test_complex_order_contract(dtype):
+    """Without NaN parts the documented complex order is NumPy's (and the golden tables');
+    with NaN parts it is lexicographic with NaN last inside each part."""
+    rng = np.random.default_rng(9)
+    a = (rng.integers(-8, 8, 6 * 500) + 1j * rng.integers(-8, 8, 6 * 500)).astype(dtype)
+    a.real[::11] = -0.0
+    assert np.array_equal(complex_lex_argsort(a, 500), np_task_sort(a, 500, True, ndim_is_1=False))
+    nan = np.nan
+    b = np.array([complex(1, nan), complex(2, 0), complex(nan, 1), complex(1, 5), complex(nan, nan), complex(nan, -1),
+                  complex(-np.inf, nan), complex(1, -np.inf)], dtype=dtype)
+    assert complex_lex_argsort(b, b.size).tolist() == [6, 7, 3, 0, 1, 5, 2, 4]
