@@ -133,6 +133,10 @@ typedef void (*b2s_barrier_fn)(void* ctx);
  * 0..nranks-1, concatenated, are the global stable sort.  The buffer belongs to the caller, as
  * with an unbound store's bind_data (sort.cu:1774-1783); *out_global_offset (may be NULL) is the
  * global position of its first element.  Synchronises the stream.
+ * The slices move between the GPUs through a copy kernel that reads the other ranks' sorted
+ * buffers in place when every rank's `alloc` returns cudaMalloc memory that CUDA IPC can export
+ * and each rank is a process of its own; otherwise, or with B2S_DIST_P2P=0 in the environment,
+ * through ncclSend/ncclRecv.  The result is the same either way.
  * Replaces SortImplBody<GPU> for unbound 1-D outputs plus sample_sort_nccl_nd
  * (src/cupynumeric/sort/sort.cu:1797-1940 and 1270-1784). */
 int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
