@@ -2,13 +2,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One "step" is one pass of the hot path (one SORT task) over one batch of seeded synthetic keys.
-At one GPU the default workload is the 1-D float32 stable argsort of 2^28 keys (N(0,1) with 0.1 %
-NaN and 1 % duplicates, int64 indices out).  ``value`` is measured with the input resident in HBM;
-``e2e`` goes through the public API with pinned host buffers (upload of the keys and download of
-the result inside the timed region).  ``--impl reference`` times the reference's CPU arithmetic
-(Thrust OpenMP back-end, every host thread) on a bounded sample of the same workload.
-Prints one JSON line (rank 0).
+One "step" is one pass of the hot path (one SORT task through the public API) over one batch of
+seeded synthetic keys.  The headline workload (``value``) is the 1-D float32 stable argsort of
+2^28 keys per GPU (N(0,1) with 0.1 % NaN and 1 % duplicates, int64 indices out); with several
+GPUs the same workload is sharded, 2^28 keys per GPU, and goes through the distributed sort.
+``value`` is measured with the input resident in HBM; ``e2e`` goes through the same API with
+pinned host buffers (upload of the keys and download of the result inside the timed region).
+
+Every number is backed by a check made in the same run (``verified``): first the same step at a
+reduced size against the CPU oracle (bit for bit; with several GPUs the rank-ordered concatenation
+against the oracle's global stable sort), then the full-size result of the warm-up on the device
+(sorted in the sort's total order, neighbouring ranks in order, element count, multiset /
+permutation fingerprints, stability of every tie).  A failed check ends the run with exit code 1.
+
+``configs`` carries the other benchmark configurations beside the headline, each timed and checked
+the same way, with its roofline (the larger of the HBM floor and the NVLink floor), the dominant
+kernel's event-timed share and, on one GPU, the CCCL library sort the reference's GPU variant
+calls (``cub_baseline``, measurement infrastructure under ``oracle/``).
+
+``--impl reference`` times the reference's CPU arithmetic (Thrust OpenMP back-end, every host
+thread) on the headline workload.  Prints one JSON line (rank 0).
 """
 from __future__ import annotations
 
@@ -26,11 +39,30 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used when MEASURED_PEAKS.json is absent
+FALLBACK_HBM_GBS = 6650.0   # used when MEASURED_PEAKS.json is absent
+NVLINK_GBS = 900.0          # per direction per GPU, the figure the roofline is defined on
+L2_BYTES = 126 << 20
 
-# DRAM bytes (read + write) of one onesweep launch per key, from the ncu capture summarised in
-# profiles/ (scaled to a full launch by the number of keys); None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_KEY = {"c1": 7.77, "c2": 13.8}  # c2: mean of the four passes (10.8, 14.8, 14.8, 14.7)
+# name -> description.  hbm_bytes: algorithmic bytes per key on one GPU / on several (the second
+# adds the k-way merge); nvlink_bytes: bytes per key that cross NVLink per direction, before the
+# (P-1)/P factor; sweep_bytes: algorithmic bytes per key of one launch of the dominant kernel.
+CONFIGS = {
+    "c1": dict(label="1-D int32 sort, N=2^{log2}, keys uniform over the full int32 range", dtype="i32", log2=24,
+               argsort=False, hbm_bytes=(36.0, 36.0), nvlink_bytes=0.0, sweep_bytes=8.0, kernel="onesweep_kernel",
+               multi="replicas"),
+    "c2": dict(label="1-D float32 stable argsort -> int64, N=2^{log2} per GPU, N(0,1) + 0.1% NaN + 1% duplicates",
+               dtype="f32", log2=28, argsort=True, hbm_bytes=(88.0, 108.0), nvlink_bytes=12.0, sweep_bytes=21.0,
+               kernel="onesweep_kernel", multi="distributed"),
+    "c3": dict(label="2-D float64 ({rows}, 4096) sort along axis -1, uniform [0,1), row blocks per GPU", dtype="f64",
+               log2=28, argsort=False, hbm_bytes=(16.0, 16.0), nvlink_bytes=0.0, sweep_bytes=16.0,
+               kernel="segsort_kernel", multi="rows"),
+    "c4": dict(label="1-D int64 distributed sort, 2^{log2} keys per GPU, Zipf(1.2) clipped to [0,2^40)", dtype="i64",
+               log2=28, argsort=False, hbm_bytes=(136.0, 152.0), nvlink_bytes=8.0, sweep_bytes=16.0,
+               kernel="onesweep_kernel", multi="distributed"),
+    "c5": dict(label="1-D uint64 distributed stable argsort -> int64, 2^{log2} keys per GPU, ascending with 1% pair swaps",
+               dtype="u64", log2=28, argsort=True, hbm_bytes=(248.0, 272.0), nvlink_bytes=16.0, sweep_bytes=31.0,
+               kernel="onesweep_kernel", multi="distributed"),
+}
 
 
 def measured_hbm_peak():
@@ -43,42 +75,226 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def ncu_traffic_bytes_per_key():
+    """DRAM bytes per key of one launch of the dominant kernel, from the committed ncu summaries."""
+    try:
+        return json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json")))["bytes_per_key_per_launch"]
+    except Exception:
+        return {}
+
+
 # ------------------------------------------------------------------------------------------------
-# workloads: name -> description used by both arms
+# inputs
 # ------------------------------------------------------------------------------------------------
-def make_workload(name: str, rank: int, nranks: int, scale_log2: int | None):
-    """Returns dict(keys=np.ndarray (this rank's tile), argsort, segment, label, bytes_per_key,
-    sweep_bytes_per_key, dtype)."""
+def config_label(name, log2, nranks):
+    c = CONFIGS[name]
+    return c["label"].format(log2=log2, rows=(1 << log2) // 4096)
+
+
+def device_input(name, log2, rank, nranks, device):
+    """This rank's tile of the configuration, drawn on the GPU."""
     from cupynumeric_b200 import workloads as w
 
+    n = 1 << log2
     if name == "c1":
-        n = 1 << (scale_log2 or 24)
-        return dict(keys=w.c1_int32_uniform(n, seed=101 + rank), argsort=False, label=f"1-D int32 sort, N=2^{n.bit_length()-1}, uniform full range, seed 101",
-                    bytes_per_key=36.0, sweep_bytes_per_key=8.0, dtype="i32")
+        return w.c1_int32_uniform_device(n, device, seed=101 + rank)
     if name == "c2":
-        n = 1 << (scale_log2 or 28)
-        # rank 0 holds the configuration's own array; further ranks draw fresh shards of the same distribution
-        return dict(keys=w.c2_float32_nan_dups(n, seed=202 + rank), argsort=True,
-                    label=f"1-D float32 stable argsort -> int64, N=2^{n.bit_length()-1}, N(0,1) + 0.1% NaN + 1% duplicates, seed 202",
-                    bytes_per_key=88.0, sweep_bytes_per_key=21.0, dtype="f32")
+        return w.c2_float32_nan_dups_device(n, device, seed=202 + rank)
     if name == "c3":
-        rows = (1 << (scale_log2 or 16)) // nranks
-        a = w.c3_float64_rows((rows, 4096), seed=303 + rank)
-        return dict(keys=a, argsort=False, label=f"2-D float64 ({rows * nranks}, 4096) sort along axis -1, uniform [0,1), row blocks per GPU",
-                    bytes_per_key=16.0, sweep_bytes_per_key=16.0, dtype="f64")
+        rows = (n // 4096) // nranks
+        return w.c3_float64_rows_device((rows, 4096), device, seed=303 + rank)
     if name == "c4":
-        n = 1 << (scale_log2 or 28)
-        return dict(keys=w.c4_int64_zipf_shard(n, rank), argsort=False,
-                    label=f"1-D int64 distributed sort, 2^{n.bit_length()-1} keys/GPU, Zipf(1.2) clipped to [0,2^40)",
-                    bytes_per_key=136.0 if nranks == 1 else 152.0, sweep_bytes_per_key=16.0, dtype="i64")
+        return w.c4_int64_zipf_shard_device(n, rank, device)
     if name == "c5":
-        n = 1 << (scale_log2 or 28)
-        return dict(keys=w.c5_uint64_nearly_sorted_shard(n, rank, nranks), argsort=True,
-                    label=f"1-D uint64 distributed stable argsort, 2^{n.bit_length()-1} keys/GPU, ascending with 1% pair swaps",
-                    bytes_per_key=248.0 if nranks == 1 else 272.0, sweep_bytes_per_key=31.0, dtype="u64")
+        import torch
+        return w.c5_uint64_nearly_sorted_shard_device(n, rank, nranks, device).view(torch.uint64)
     raise SystemExit(f"unknown workload {name}")
 
 
+def host_input(name, log2, rank, nranks):
+    """The same tile from the NumPy generators (reduced-size checks, reference arm)."""
+    from cupynumeric_b200 import workloads as w
+
+    n = 1 << log2
+    if name == "c1":
+        return w.c1_int32_uniform(n, seed=101 + rank)
+    if name == "c2":
+        return w.c2_float32_nan_dups(n, seed=202 + rank)
+    if name == "c3":
+        return w.c3_float64_rows(((n // 4096) // nranks, 4096), seed=303 + rank)
+    if name == "c4":
+        return w.c4_int64_zipf_shard(n, rank)
+    if name == "c5":
+        return w.c5_uint64_nearly_sorted_shard(n, rank, nranks)
+    raise SystemExit(f"unknown workload {name}")
+
+
+# ------------------------------------------------------------------------------------------------
+# checks (torch ops on the device are the checker here, never the thing measured)
+# ------------------------------------------------------------------------------------------------
+_MIN64 = -(1 << 63)
+
+
+def ordered_i64(t):
+    """int64 tensor whose signed order is the sort's total order of ``t``: integers by value,
+    floats as -inf < .. < -0.0 == +0.0 < .. < +inf < NaN (all NaNs equal)."""
+    import torch
+
+    if t.dtype == torch.uint64:
+        return t.view(torch.int64) ^ _MIN64
+    if t.dtype in (torch.int8, torch.int16, torch.int32, torch.int64, torch.uint8, torch.bool, torch.uint16, torch.uint32):
+        if t.dtype == torch.uint16:
+            return t.view(torch.int16).to(torch.int64) & 0xFFFF
+        if t.dtype == torch.uint32:
+            return t.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        return t.to(torch.int64)
+    if t.dtype in (torch.float16, torch.float32, torch.float64):
+        v = t.to(torch.float64).view(torch.int64) if t.dtype != torch.float64 else t.view(torch.int64)
+        o = torch.where(v < 0, (~v) ^ _MIN64, v)
+        o = torch.where(t == 0, torch.zeros_like(o), o)
+        return torch.where(t != t, torch.full_like(o, (1 << 63) - 1), o)
+    raise TypeError(t.dtype)
+
+
+def _mix(x, c):
+    """A 64-bit mixing function in wrapping int64 arithmetic."""
+    x = x * c
+    x = x ^ (x >> 31)
+    x = x * -7046029254386353131
+    return x ^ (x >> 29)
+
+
+def fingerprint(x_i64):
+    """Order-independent 2 x 64-bit fingerprint of a multiset of int64 values (wrapping sums)."""
+    import torch
+
+    return torch.stack([_mix(x_i64, -4417276706812531889).sum(), _mix(x_i64 ^ 0x5DEECE66D, 7640891576956012809).sum()])
+
+
+def check_full(name, tile, result, result_lo, rank, nranks, dist):
+    """Properties of a full-size result that together pin it: returns (ok, detail).  ``tile`` is
+    this rank's input, ``result`` this rank's part of the output, ``result_lo`` its global start."""
+    import torch
+
+    c = CONFIGS[name]
+    dev = tile.device
+    multi = nranks > 1 and c["multi"] == "distributed"
+
+    def allsum(v):
+        if multi:
+            dist.all_reduce(v)
+        return v
+
+    detail = {}
+    if tile.ndim == 2:  # independent rows: every row sorted, every row a permutation of its input
+        o_out = ordered_i64(result)
+        sorted_ok = bool((o_out[:, 1:] >= o_out[:, :-1]).all())
+        same = bool((_mix(tile.view(torch.int64), -4417276706812531889).sum(1) ==
+                     _mix(result.view(torch.int64), -4417276706812531889).sum(1)).all())
+        detail = {"rows_sorted": sorted_ok, "rows_same_multiset": same}
+        return sorted_ok and same, detail
+
+    n_in = torch.tensor([tile.numel()], dtype=torch.int64, device=dev)
+    n_out = torch.tensor([result.numel()], dtype=torch.int64, device=dev)
+    total_in, total_out = int(allsum(n_in)), int(allsum(n_out))
+    detail["count"] = total_in == total_out
+    o_in = ordered_i64(tile)
+    if not c["argsort"]:
+        o_out = ordered_i64(result)
+        detail["sorted"] = bool((o_out[1:] >= o_out[:-1]).all()) if o_out.numel() > 1 else True
+        bits = lambda t: t.view({1: torch.int8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[t.element_size()]).to(torch.int64)
+        detail["same_multiset"] = bool((allsum(fingerprint(bits(tile))) == allsum(fingerprint(bits(result)))).all())
+        first = o_out[:1] if o_out.numel() else torch.zeros(1, dtype=torch.int64, device=dev)
+        last = o_out[-1:] if o_out.numel() else torch.zeros(1, dtype=torch.int64, device=dev)
+        edge = torch.cat([first, last, n_out * 0 + result.numel()])
+    else:
+        # the keys of the whole array, so that every index of my part can be looked up
+        if multi:
+            parts = [torch.empty_like(o_in) for _ in range(nranks)]
+            dist.all_gather(parts, o_in)
+            o_all = torch.cat(parts)
+            del parts
+        else:
+            o_all = o_in
+        idx = result
+        in_range = bool(((idx >= 0) & (idx < total_in)).all()) if idx.numel() else True
+        detail["indices_in_range"] = in_range
+        if not in_range:
+            return False, detail
+        ko = o_all[idx]
+        if idx.numel() > 1:
+            detail["sorted_and_stable"] = bool(((ko[1:] > ko[:-1]) | ((ko[1:] == ko[:-1]) & (idx[1:] > idx[:-1]))).all())
+        else:
+            detail["sorted_and_stable"] = True
+        mine = torch.arange(result_lo, result_lo + idx.numel(), dtype=torch.int64, device=dev)
+        detail["permutation"] = bool((allsum(fingerprint(idx)) == allsum(fingerprint(mine))).all())
+        first = torch.stack([ko[0], idx[0]]) if idx.numel() else torch.zeros(2, dtype=torch.int64, device=dev)
+        last = torch.stack([ko[-1], idx[-1]]) if idx.numel() else torch.zeros(2, dtype=torch.int64, device=dev)
+        edge = torch.cat([first, last, n_out * 0 + idx.numel()])
+        del o_all, ko
+    if multi:
+        edges = [torch.empty_like(edge) for _ in range(nranks)]
+        dist.all_gather(edges, edge)
+        rows = [e.tolist() for e in edges]
+        ok, prev = True, None
+        start = 0
+        for r, e in enumerate(rows):
+            cnt = e[-1]
+            if r == rank and start != result_lo:
+                ok = False  # the reported global start must be the sum of the lower ranks' lengths
+            start += cnt
+            if cnt == 0:
+                continue
+            half = (len(e) - 1) // 2
+            lo_key, hi_key = tuple(e[:half]), tuple(e[half:2 * half])
+            if prev is not None and not (prev <= lo_key if not c["argsort"] else prev < lo_key):
+                ok = False
+            prev = hi_key
+        detail["ranks_in_order"] = ok
+    return all(detail.values()), detail
+
+
+def check_small(name, rank, nranks, dist, num, log2=20):
+    """The step at a reduced size against the CPU oracle, bit for bit (rank 0 compares)."""
+    from oracle import thrust_task_sort
+
+    c = CONFIGS[name]
+    if name == "c3":
+        log2 = 12 + 8  # 256 rows in all
+    shard = host_input(name, log2, rank, nranks)
+    multi = nranks > 1 and c["multi"] == "distributed"
+    lo = rank * shard.shape[0] if multi else 0
+    arr = num.array(shard, global_lo=lo)
+    res = num.argsort(arr, kind="stable") if c["argsort"] else num.sort(arr)
+    got = res.to_numpy()
+    if not multi:
+        seg = shard.shape[-1]
+        want_k, want_i = thrust_task_sort(shard, seg, c["argsort"], ndim_is_1=shard.ndim == 1)
+        want = want_i if c["argsort"] else want_k
+        ok = np.array_equal(got.reshape(-1).view(np.uint8), want.reshape(-1).view(np.uint8))
+        if nranks > 1:
+            flags = [None] * nranks
+            dist.all_gather_object(flags, bool(ok))
+            ok = all(flags)
+        return bool(ok)
+    shards, parts, starts = [None] * nranks, [None] * nranks, [None] * nranks
+    dist.all_gather_object(shards, shard)
+    dist.all_gather_object(parts, got)
+    dist.all_gather_object(starts, int(res.global_lo))
+    ok = True
+    if rank == 0:
+        whole = np.concatenate(shards)
+        want_k, want_i = thrust_task_sort(whole, whole.size, c["argsort"])
+        want = want_i if c["argsort"] else want_k
+        cat = np.concatenate(parts)
+        ok = cat.shape == want.shape and np.array_equal(cat.view(np.uint8), want.view(np.uint8))
+        ok = ok and starts == [int(x) for x in np.cumsum([0] + [len(p) for p in parts])[:-1]]
+    flag = [bool(ok)]
+    dist.broadcast_object_list(flag, src=0)
+    return flag[0]
+
+
+# ------------------------------------------------------------------------------------------------
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -129,212 +345,330 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_reference_time(keys: np.ndarray, argsort: bool, sample: int, steps: int, warmup: int):
-    """Times the reference's CPU arithmetic (OpenMP back-end, all host threads) on the first
-    ``sample`` keys (whole rows for 2-D inputs).  Returns (Gkeys/s, seconds per step, threads)."""
-    from oracle import num_threads, thrust_task_sort
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline
+# ------------------------------------------------------------------------------------------------
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
 
-    if keys.ndim == 2:
-        rows = max(1, min(keys.shape[0], sample // keys.shape[1]))
-        part, segment, one_d = keys[:rows], keys.shape[1], False
-    else:
-        part, segment, one_d = keys[:sample], min(sample, keys.size), True
-    times = []
+
+def cpu_reference_time(keys: np.ndarray, argsort: bool, steps: int, warmup: int, budget_s: float):
+    """Times the reference's CPU arithmetic (OpenMP back-end, all host threads) on ``keys`` (whole
+    rows for 2-D inputs).  Stops early when ``budget_s`` is spent.  Returns (Gkeys/s, seconds per
+    step, threads, steps timed)."""
+    from oracle import num_threads, set_num_threads, thrust_task_sort
+
+    set_num_threads(host_threads())  # launchers export OMP_NUM_THREADS=1 to their children
+    segment, one_d = (keys.shape[1], False) if keys.ndim == 2 else (keys.size, True)
+    times, t_start = [], time.perf_counter()
     for i in range(warmup + steps):
         t0 = time.perf_counter()
-        thrust_task_sort(part, segment, argsort, ndim_is_1=one_d, backend="omp")
+        thrust_task_sort(keys, segment, argsort, ndim_is_1=one_d, backend="omp")
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
+        if times and time.perf_counter() - t_start + dt > budget_s:
+            break
+    if not times:
+        times = [dt]
     per = float(np.mean(times))
-    return part.size / per / 1e9, per, num_threads()
+    return keys.size / per / 1e9, per, num_threads(), len(times)
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    wl = make_workload(args.workload, 0, 1, args.scale_log2)
-    sample = 1 << args.cpu_sample_log2
-    gk, per, threads = cpu_reference_time(wl["keys"], wl["argsort"], sample, args.steps, min(args.warmup, 1))
-    n = min(sample, wl["keys"].size)
+    name = args.workload
+    log2 = args.scale_log2 or CONFIGS[name]["log2"]
+    keys = host_input(name, log2, 0, 1)
+    gk, per, threads, done = cpu_reference_time(keys, CONFIGS[name]["argsort"], args.steps, args.warmup, args.reference_budget_s)
     line = {
         "impl": "reference", "metric": "sorted Gkeys/s", "value": gk, "unit": "Gkeys/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": per * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["label"], "sample": f"first {n} keys of the workload per step"},
+        "steps": done, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": CONFIGS[name]["dtype"], "data": "synthetic",
+        "config": {"workload": config_label(name, log2, 1), "keys_per_step": int(keys.size),
+                   "note": "one host runs the CPU arm whatever --gpus says: all keys of one GPU's shard per step"},
         "cpu_baseline": {"value": gk, "unit": "Gkeys/s", "cores": threads, "kind": "port",
-                         "sample": f"thrust::omp::par stable sort of the first {n} keys, {args.steps} steps"},
+                         "sample": f"thrust::omp::par stable sort of all {keys.size} keys of the workload, {done} steps"},
         "e2e": {"value": gk, "unit": "Gkeys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+KINDS = ["hist", "scan", "sweep", "fixup", "segsort", "unit", "dist", "merge", "xchg"]
 
-    import cupynumeric_b200 as num
-    from cupynumeric_b200 import _lib
-    from cupynumeric_b200._thunk._sort import local_sort_tile
 
-    nranks = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    if nranks > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    lib = _lib.lib()
+class Bench:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
 
-    wl = make_workload(args.workload, rank, nranks, args.scale_log2)
-    host = wl["keys"]
-    n_local = host.size
-    distributed = nranks > 1 and host.ndim == 1
-    arr = num.array(host, global_lo=rank * n_local if host.ndim == 1 else 0)
-    tile = arr.torch()
-    out = torch.empty(tile.shape, dtype=torch.int64 if wl["argsort"] else tile.dtype, device=tile.device)
+        import cupynumeric_b200 as num
+        from cupynumeric_b200 import _lib
 
-    def step():
-        if distributed:
-            r = num.argsort(arr, kind="stable") if wl["argsort"] else num.sort(arr)
-            return r
-        return local_sort_tile(tile, wl["argsort"], True, index_offset=0, out=out)
+        self.args, self.torch, self.dist, self.num = args, torch, dist, num
+        self.nranks = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        if self.nranks > 1:
+            dist.init_process_group("nccl", device_id=self.device)
+        self.lib = _lib.lib()
+        self.peak, self.peak_kind = measured_hbm_peak()
+        self.flush_buf = None
 
-    def barrier():
-        if nranks > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.nranks > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        if self.nranks > 1:
+            t = self.torch.tensor([ms], device=self.device, dtype=self.torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def flush_l2(self):
+        if self.flush_buf is None:
+            self.flush_buf = self.torch.empty(256 << 20, dtype=self.torch.uint8, device=self.device)
+        self.flush_buf.zero_()
+
+    def kernel_breakdown(self, steps):
+        out = {}
+        for k, nm in enumerate(KINDS):
+            tot, cnt = ctypes.c_double(0), ctypes.c_ulonglong(0)
+            self.lib.b2s_profile_read(k, ctypes.byref(tot), ctypes.byref(cnt))
+            if cnt.value:
+                out[nm] = {"ms_per_step": tot.value / steps, "launches_per_step": cnt.value / steps,
+                           "avg_launch_ms": tot.value / cnt.value}
+        return out
+
+    def run_config(self, name, log2, headline=False):
+        """Times one configuration; returns its record."""
+        torch, num, args = self.torch, self.num, self.args
+        c = CONFIGS[name]
+        nranks, rank = self.nranks, self.rank
+        multi = nranks > 1 and c["multi"] == "distributed"
+        rec = {"workload": config_label(name, log2, nranks), "multi_gpu": c["multi"] if nranks > 1 else "one GPU"}
+
+        small_ok = True if args.no_verify else check_small(name, rank, nranks, self.dist, num)
+        tile = device_input(name, log2, rank, nranks, self.device)
+        n_local = tile.numel()
+        arr = num.array(tile, global_lo=rank * n_local if multi else 0)
+        flush = tile.numel() * tile.element_size() <= L2_BYTES
+
+        def step():
+            return num.argsort(arr, kind="stable") if c["argsort"] else num.sort(arr)
+
+        res = None
+        for _ in range(args.warmup):
+            res = step()
+        self.barrier()
+        full_ok, detail = (True, {}) if args.no_verify else check_full(name, tile, res.torch(), res.global_lo if multi else 0,
+                                                                        rank, nranks, self.dist)
+        del res
+        sampler = ClockSampler(self.local_rank) if (headline and rank == 0) else None
+        if sampler:
+            sampler.start()
+        launches0 = self.lib.b2s_launch_count(-1)
+        self.barrier()
+        ms = 0.0
+        if flush:
+            for _ in range(args.steps):
+                self.flush_l2()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                step()
+                e1.record()
+                torch.cuda.synchronize()
+                ms += e0.elapsed_time(e1)
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                step()
+            e1.record()
+            self.barrier()
+            ms = e0.elapsed_time(e1)
+        self.barrier()
+        clocks = sampler.stop() if sampler else None
+        launches = int(self.lib.b2s_launch_count(-1) - launches0)
+        ms = self.max_over_ranks(ms) / args.steps
+        # the same steps once more with one CUDA-event pair around every launch: where the time goes
+        psteps = max(1, min(args.steps, 5))
+        self.lib.b2s_profile_enable(1)
+        for _ in range(psteps):
+            if flush:
+                self.flush_l2()
+            step()
         torch.cuda.synchronize()
+        kernels = self.kernel_breakdown(psteps)
+        self.lib.b2s_profile_enable(0)
+        self.barrier()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    launches0 = lib.b2s_launch_count(-1)
-    lib.b2s_profile_enable(1)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        step()
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else None
-    launches = lib.b2s_launch_count(-1) - launches0
-    kind = _lib.K_SEGSORT if host.ndim == 2 else _lib.K_SWEEP
-    tot, cnt = ctypes.c_double(0), ctypes.c_ulonglong(0)
-    lib.b2s_profile_read(kind, ctypes.byref(tot), ctypes.byref(cnt))
-    lib.b2s_profile_enable(0)
-    if nranks > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    total_keys = n_local * nranks
-    value = total_keys * args.steps / (ms * 1e-3) / 1e9
+        total_keys = n_local * nranks
+        gkeys = total_keys / (ms * 1e-3) / 1e9
+        hbm_bytes = c["hbm_bytes"][1 if multi else 0]
+        t_hbm = hbm_bytes * n_local / (self.peak * 1e9)
+        t_nvl = c["nvlink_bytes"] * (nranks - 1) / nranks * n_local / (NVLINK_GBS * 1e9) if multi else 0.0
+        floor = max(t_hbm, t_nvl)
+        rec.update({
+            "keys_per_gpu": n_local, "ms_per_step": ms, "gkeys_per_s": gkeys,
+            "verified": {"ok": bool(small_ok and full_ok), "oracle_bit_exact_at_reduced_size": bool(small_ok),
+                         "full_size_properties": detail},
+            "roofline": {"bound": "hbm" if t_hbm >= t_nvl else "nvlink", "hbm_bytes_per_key": hbm_bytes,
+                         "nvlink_bytes_per_key_per_direction": c["nvlink_bytes"] * (nranks - 1) / nranks if multi else 0.0,
+                         "floor_ms": floor * 1e3, "frac": floor * 1e3 / ms, "hbm_peak_gbs": self.peak,
+                         "peak_source": f"of {self.peak_kind}", "nvlink_gbs": NVLINK_GBS,
+                         "frac_of_8TBs": (max(hbm_bytes * n_local / 8e12, t_nvl)) * 1e3 / ms},
+            "kernels": kernels, "gpu_launches_per_step": launches / args.steps,
+            "l2": "input smaller than L2: a 256 MB buffer is written between timed steps" if flush
+                  else "input larger than the 126 MB L2, no flush needed",
+        })
+        if multi:
+            rec["exchange"] = os.environ.get("B2S_DIST_P2P", "1") != "0" and "peer" or "nccl"
+        dom = {"onesweep_kernel": "sweep", "segsort_kernel": "segsort"}[c["kernel"]]
+        if dom in kernels:
+            avg_ms = kernels[dom]["avg_launch_ms"]
+            achieved = c["sweep_bytes"] * n_local / (avg_ms * 1e-3) / 1e9
+            traffic = ncu_traffic_bytes_per_key().get(name)
+            rec["dominant_kernel"] = {"bound": "hbm", "kernel": c["kernel"], "achieved": achieved, "peak": self.peak,
+                                      "unit": "GB/s", "frac": achieved / self.peak, "peak_source": f"of {self.peak_kind}",
+                                      "avg_launch_ms": avg_ms, "launches_per_step": kernels[dom]["launches_per_step"],
+                                      "algorithmic_bytes_per_launch": c["sweep_bytes"] * n_local,
+                                      "traffic": traffic * n_local if traffic else None}
+        if nranks == 1 and not args.no_cub:
+            rec["cub_baseline"] = self.cub_baseline(tile, c["argsort"])
+        rec["_clocks"], rec["_launches"], rec["_tile"] = clocks, launches, tile
+        return rec
 
-    # ---- end to end through the public API with pinned host buffers ----
-    e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    pinned_in = torch.from_numpy(host.view(np.int32 if host.dtype.itemsize == 4 else np.int64)).pin_memory()
-    host_in = pinned_in.numpy().view(host.dtype)
-    res_dtype = np.int64 if wl["argsort"] else host.dtype
-    e2e_ms, h2d, d2h = None, int(host.nbytes), None
-    if not distributed:
-        pinned_out = torch.empty(host.shape, dtype=torch.int64 if res_dtype == np.int64 else pinned_in.dtype).pin_memory()
+    def cub_baseline(self, tile, argsort):
+        """The CCCL library sort the reference's GPU variant calls, on the same tile."""
+        try:
+            from oracle import cub_baseline as cb
+            if not cb.available():
+                return {"unavailable": "oracle/libcub_baseline.so is not built"}
+            ms, _ = cb.time_sort(tile, argsort,
+                                 steps=max(1, min(self.args.steps, 5)), warmup=2)
+            return {"ms_per_step": ms, "gkeys_per_s": tile.numel() / (ms * 1e-3) / 1e9,
+                    "what": "cub::DeviceRadixSort / DeviceSegmentedRadixSort (+ index fill for argsort), CCCL of the CUDA toolkit"}
+        except Exception as e:  # the baseline is optional evidence, not part of the product
+            return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+    def run_e2e(self, name, log2, tile):
+        """The same step through the public API with pinned host buffers on both sides."""
+        torch, num, args = self.torch, self.num, self.args
+        c = CONFIGS[name]
+        nranks, rank = self.nranks, self.rank
+        multi = nranks > 1 and c["multi"] == "distributed"
+        n_local = tile.numel()
+        sview = {torch.uint64: torch.int64, torch.uint32: torch.int32, torch.uint16: torch.int16}.get(tile.dtype, tile.dtype)
+        pinned_in = torch.empty(tile.shape, dtype=sview, pin_memory=True)
+        pinned_in.copy_(tile.view(sview))
+        np_dtype = {"i32": np.int32, "f32": np.float32, "f64": np.float64, "i64": np.int64, "u64": np.uint64}[c["dtype"]]
+        host_in = pinned_in.numpy().view(np_dtype)
+        res_dtype = np.int64 if c["argsort"] else np_dtype
+        cap = int(n_local * 1.5) + 1024 if multi else n_local
+        pinned_out = torch.empty(cap if tile.ndim == 1 else tile.shape, dtype=torch.int64 if c["argsort"] else sview, pin_memory=True)
         host_out = pinned_out.numpy().view(res_dtype)
-        d2h = int(host_out.nbytes)
+        got = [n_local]
 
         def e2e_step():
-            a = num.array(host_in)
-            r = num.argsort(a, kind="stable") if wl["argsort"] else num.sort(a)
-            r.to_numpy(out=host_out)
-
-        e2e_step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        e1.record()
-        barrier()
-        e2e_ms = e0.elapsed_time(e1)
-    else:
-        # each rank's part of the result has its own length: a pinned buffer with head-room
-        cap = int(n_local * 1.5) + 1024
-        pinned_out = torch.empty(cap, dtype=torch.int64 if res_dtype == np.int64 else pinned_in.dtype).pin_memory()
-        host_out = pinned_out.numpy().view(res_dtype)
-        got = [0]
-
-        def e2e_step():
-            a = num.array(host_in, global_lo=rank * n_local)
-            r = num.argsort(a, kind="stable") if wl["argsort"] else num.sort(a)
+            a = num.array(host_in, global_lo=rank * n_local if multi else 0)
+            r = num.argsort(a, kind="stable") if c["argsort"] else num.sort(a)
             got[0] = r.size
-            r.to_numpy(out=host_out[: r.size])
+            r.to_numpy(out=host_out[: r.size] if tile.ndim == 1 else host_out)
 
+        steps = max(1, min(args.steps, args.e2e_steps))
         e2e_step()
-        barrier()
+        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(e2e_steps):
+        for _ in range(steps):
             e2e_step()
         e1.record()
-        barrier()
-        d2h = int(got[0]) * np.dtype(res_dtype).itemsize
-        t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = total_keys * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        self.barrier()
+        ms = self.max_over_ranks(e0.elapsed_time(e1)) / steps
+        h2d, d2h = int(host_in.nbytes), int(got[0]) * np.dtype(res_dtype).itemsize
+        return {"value": n_local * nranks / (ms * 1e-3) / 1e9, "unit": "Gkeys/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
+                "host_copy_gbs_per_rank": (h2d + d2h) / (ms * 1e-3) / 1e9,
+                "note": "per rank: pinned host -> device copy of the keys, the sort, device -> pinned host copy of the result; "
+                        "all ranks of one box share the host's memory and PCIe root"}
 
-    if rank != 0:
-        if nranks > 1:
-            dist.destroy_process_group()
-        return
 
-    peak, peak_kind = measured_hbm_peak()
-    launches_k = int(cnt.value)
-    roofline = None
-    if launches_k:
-        avg_ms = tot.value / launches_k
-        # algorithmic bytes of one launch of the dominant kernel: keys one launch processes x bytes per key
-        keys_one_launch = n_local
-        achieved = wl["sweep_bytes_per_key"] * keys_one_launch / (avg_ms * 1e-3) / 1e9
-        traffic_pk = NCU_TRAFFIC_BYTES_PER_KEY.get(args.workload)
-        roofline = {"bound": "hbm", "kernel": "segsort_kernel" if host.ndim == 2 else "onesweep_kernel",
-                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "peak_source": f"of {peak_kind}", "avg_launch_ms": avg_ms, "launches_timed": launches_k,
-                    "algorithmic_bytes_per_launch": wl["sweep_bytes_per_key"] * keys_one_launch,
-                    "traffic": traffic_pk * keys_one_launch if traffic_pk else None}
-    job_gbs = wl["bytes_per_key"] * n_local * args.steps / (ms * 1e-3) / 1e9
-
+def run_ours(args):
+    b = Bench(args)
+    torch, dist = b.torch, b.dist
+    name = args.workload
+    log2 = args.scale_log2 or CONFIGS[name]["log2"]
+    head = b.run_config(name, log2, headline=True)
+    tile = head.pop("_tile")
+    clocks, launches = head.pop("_clocks"), head.pop("_launches")
+    e2e = b.run_e2e(name, log2, tile)
+    n_local = tile.numel()
     cpu = None
-    if nranks == 1 and not args.no_cpu_baseline:
-        sample = 1 << args.cpu_sample_log2
-        gk, per, threads = cpu_reference_time(host, wl["argsort"], sample, 1, 0)
+    if b.nranks == 1 and b.rank == 0 and not args.no_cpu_baseline:
+        sample = min(1 << args.cpu_sample_log2, n_local)
+        host = tile.reshape(-1)[:sample].cpu()
+        host = host.numpy() if host.dtype != torch.uint64 else host.view(torch.int64).numpy().view(np.uint64)
+        if tile.ndim == 2:
+            host = host.reshape(-1, tile.shape[1])
+        gk, per, threads, _ = cpu_reference_time(host, CONFIGS[name]["argsort"], 1, 0, 60.0)
         cpu = {"value": gk, "unit": "Gkeys/s", "cores": threads, "kind": "port",
-               "sample": f"thrust::omp::par stable sort of the first {min(sample, host.size)} keys of the workload, 1 step ({per:.2f} s)"}
+               "sample": f"thrust::omp::par stable sort of the first {host.size} keys of the workload, 1 step ({per:.2f} s)"}
+    del tile
+    torch.cuda.empty_cache()
 
-    line = {
-        "metric": "sorted Gkeys/s", "value": value, "unit": "Gkeys/s", "n_gpus": nranks, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
-        "config": {"workload": wl["label"], "keys_per_gpu": n_local,
-                   "l2": "inputs larger than the 126 MB L2, no flush needed" if host.nbytes > (126 << 20)
-                   else "input smaller than L2; every step re-reads it after the sort's own temporaries evicted it"},
-        "roofline": roofline,
-        "job_roofline": {"algorithmic_bytes_per_key": wl["bytes_per_key"], "achieved": job_gbs, "peak": peak,
-                         "unit": "GB/s", "frac": job_gbs / peak, "peak_source": f"of {peak_kind}",
-                         "frac_of_8TBs": job_gbs / 8000.0},
-        "cpu_baseline": cpu,
-        "e2e": {"value": e2e_value, "unit": "Gkeys/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
-        "gpu_launches": int(launches),
-        "clocks": clocks,
-    }
-    print(json.dumps(line))
-    if nranks > 1:
+    configs = {}
+    if not args.no_configs:
+        for other in [x for x in args.configs.split(",") if x and x != name]:
+            rec = b.run_config(other, args.scale_log2 or CONFIGS[other]["log2"])
+            for k in ("_tile", "_clocks", "_launches"):
+                rec.pop(k, None)
+            configs[other] = rec
+            torch.cuda.empty_cache()
+
+    all_ok = head["verified"]["ok"] and all(r["verified"]["ok"] for r in configs.values())
+    if b.rank == 0:
+        dom = head.get("dominant_kernel")
+        line = {
+            "metric": "sorted Gkeys/s", "value": head["gkeys_per_s"], "unit": "Gkeys/s", "n_gpus": b.nranks,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": CONFIGS[name]["dtype"], "data": "synthetic",
+            "config": {"workload": head["workload"], "keys_per_gpu": n_local, "l2": head["l2"],
+                       "multi_gpu": head["multi_gpu"], "exchange": head.get("exchange")},
+            "verified": head["verified"],
+            "roofline": dom,
+            "job_roofline": head["roofline"],
+            "kernels": head["kernels"],
+            "cub_baseline": head.get("cub_baseline"),
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "configs": configs,
+        }
+        print(json.dumps(line))
+    if b.nranks > 1:
+        dist.barrier()
+        try:
+            from cupynumeric_b200._dist import destroy_comm
+            destroy_comm()
+        except Exception:
+            pass
         dist.destroy_process_group()
+    if not all_ok:
+        sys.exit(1)
 
 
 def main():
@@ -343,14 +677,20 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=["c1", "c2", "c3", "c4", "c5"])
-    ap.add_argument("--scale-log2", type=int, default=None, help="log2 of the key count (per GPU); default: the configuration's size")
-    ap.add_argument("--cpu-sample-log2", type=int, default=25)
+    ap.add_argument("--workload", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--scale-log2", type=int, default=None, help="log2 of the key count per GPU; default: the configuration's size")
+    ap.add_argument("--configs", default="c1,c3,c4,c5", help="configurations reported beside the headline")
+    ap.add_argument("--cpu-sample-log2", type=int, default=26)
+    ap.add_argument("--reference-budget-s", type=float, default=240.0, help="the reference arm stops starting new steps after this")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true")
+    ap.add_argument("--no-cub", action="store_true")
+    ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--lean", action="store_true", help="headline only: no other configurations, checks or baselines (profiling runs)")
     args = ap.parse_args()
-    if args.workload is None:
-        args.workload = "c2"
+    if args.lean:
+        args.no_cpu_baseline = args.no_configs = args.no_cub = args.no_verify = True
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":

@@ -46,6 +46,7 @@ class ndarray:
     def to_numpy(self, out: np.ndarray | None = None) -> np.ndarray:
         """Copies this process's tile to host memory (into ``out`` when given)."""
         t = self._thunk.base
+        runtime.raise_pending()
         if out is None:
             return t.cpu().numpy() if t.dtype not in (torch.uint16, torch.uint32, torch.uint64) \
                 else t.view(_SIGNED_VIEW[t.dtype]).cpu().numpy().view(self.dtype)

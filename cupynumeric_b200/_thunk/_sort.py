@@ -47,6 +47,8 @@ def local_sort_tile(tile: torch.Tensor, argsort: bool, stable: bool, index_offse
                             int(tile.ndim == 1), int(stable), ws.data_ptr(), ws.numel(),
                             runtime.stream_handle())
     _lib.check(st, "b2s_local_sort")
+    if tile.dtype != torch.complex128:  # (its inner sorts keep their control blocks elsewhere)
+        runtime.note_sort(ws)
     return out
 
 
@@ -54,7 +56,7 @@ def sort_flattened(output: DeferredArray, input: DeferredArray, argsort: bool, s
     flat = input.reshape((input.size,), order="C")
     result = create_deferred_thunk(flat.shape, dtype=output.dtype)
     sort_deferred(result, flat, argsort, stable=stable)
-    output.base = result.base
+    output.base, output.global_lo, output.tiled_axis = result.base, result.global_lo, result.tiled_axis
 
 
 def sort_swapped(output: DeferredArray, input: DeferredArray, argsort: bool, sort_axis: int,

@@ -202,8 +202,10 @@ constexpr int DIST_PHASES = B2S_DIST_PHASES;
 static cudaStream_t exchange_stream()
 {
   static cudaStream_t streams[64] = {};
+  static std::mutex mu;  // two host threads may ask for the same device's stream together
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
   if (streams[dev] == nullptr) {
     if (cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
   }

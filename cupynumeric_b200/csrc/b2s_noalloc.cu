@@ -8,6 +8,8 @@
 // every GPU loading this library carries from load to exit.
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "../../include/b200sort.h"
 
 namespace {
@@ -21,6 +23,23 @@ constexpr int MAX_DEVICES = 64;
 // Device address of g_scratch per device, filled on the first call made on that device.  In
 // host code `g_scratch` itself is only a handle for the runtime, not an address a kernel may use.
 unsigned char* g_scratch_addr[MAX_DEVICES] = {};
+std::mutex g_setup_mutex;  // two host threads may make their first call on a device together
+
+// One-time set-up per device, with that device current: looks the array's device address up.
+int scratch_of_current_device(unsigned char** out)
+{
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B2S_ERR_CUDA;
+  if (dev < 0 || dev >= MAX_DEVICES) return B2S_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_scratch) != cudaSuccess || p == nullptr) return B2S_ERR_CUDA;
+    g_scratch_addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = g_scratch_addr[dev];
+  return B2S_OK;
+}
 
 }  // namespace
 
@@ -32,17 +51,20 @@ extern "C" int b2s_local_sort_noalloc(int dtype, const void* keys_in, void* keys
   int rc      = b2s_workspace_bytes(dtype, volume, segment, idx_out != nullptr, &need);
   if (rc != B2S_OK) return rc;
   if (need > (size_t)B2S_NOALLOC_SCRATCH_BYTES) return B2S_ERR_WORKSPACE;  // problem too large for the fixed scratch
-
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return B2S_ERR_CUDA;
-  if (dev < 0 || dev >= MAX_DEVICES) return B2S_ERR_UNSUPPORTED;
-  if (g_scratch_addr[dev] == nullptr) {
-    // one-time set-up for this device, with this device current
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_scratch) != cudaSuccess || p == nullptr) return B2S_ERR_CUDA;
-    g_scratch_addr[dev] = static_cast<unsigned char*>(p);
-  }
+  unsigned char* scratch = nullptr;
+  rc = scratch_of_current_device(&scratch);
+  if (rc != B2S_OK) return rc;
   // b2s_local_sort clears the control block and the look-back table of the scratch on every call
-  return b2s_local_sort(dtype, keys_in, keys_out, idx_out, volume, segment, index_offset, ndim_is_1, 1,
-                        g_scratch_addr[dev], (size_t)B2S_NOALLOC_SCRATCH_BYTES, cuda_stream);
+  return b2s_local_sort(dtype, keys_in, keys_out, idx_out, volume, segment, index_offset, ndim_is_1, 1, scratch,
+                        (size_t)B2S_NOALLOC_SCRATCH_BYTES, cuda_stream);
+}
+
+// The status word of the last b2s_local_sort_noalloc on this device sits at the head of the same
+// array; this reads it back the way b2s_check_status does for a caller-owned workspace.
+extern "C" int b2s_noalloc_check_status(void* cuda_stream)
+{
+  unsigned char* scratch = nullptr;
+  const int rc = scratch_of_current_device(&scratch);
+  if (rc != B2S_OK) return rc;
+  return b2s_check_status(scratch, cuda_stream);
 }

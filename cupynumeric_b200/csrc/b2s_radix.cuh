@@ -14,6 +14,9 @@ namespace b2s {
 // Warp-level shortcut: when all 32 lanes hold the same digit (sorted input, constant high
 // bytes) one lane adds 32 instead of 32 serialised shared-memory atomics.
 // ---------------------------------------------------------------------------------------------
+#ifndef B2S_HIST_FORM
+#define B2S_HIST_FORM 0
+#endif
 template <int KB, int XF>
 __device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], typename KeyOf<KB>::type raw)
 {
@@ -37,9 +40,6 @@ __device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], ty
   }
 }
 
-#ifndef B2S_HIST_FORM
-#define B2S_HIST_FORM 0
-#endif
 constexpr int HIST_THREADS = 512;
 
 template <int KB, int XF>
@@ -319,7 +319,6 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 
   const PassDesc pd = ctrl->pass[pass];
   if (!pd.active) return;
-  if (ld_relaxed(&ctrl->abort)) return;
 
   extern __shared__ __align__(128) unsigned char smem[];
   K* stage_keys          = reinterpret_cast<K*>(smem);
@@ -336,12 +335,15 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
   const DigitSel ds = make_digit_sel<KB, XF>(pass);
 
   if (tid == 0) {
+    // one thread reads the abort flag for the whole CTA, so that all of its threads leave together
+    misc[1] = ld_relaxed(&ctrl->abort);
     misc[0] = atomicAdd(&ctrl->tile_counter[pass], 1u);
     mbar_init(bar, 1);
     fence_mbar_init();
   }
   for (int i = tid; i < (ROWS + (B2S_RANK_ATOMIC ? S::WARPS : 0)) * RADIX; i += THREADS) hist[i] = 0;
   __syncthreads();
+  if (misc[1]) return;
   const unsigned int tile = misc[0];
   const unsigned int seg  = tile / geo.tiles_per_seg;
   if (seg >= geo.nseg) return;  // more CTAs than tiles

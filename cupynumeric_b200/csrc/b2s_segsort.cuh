@@ -63,26 +63,29 @@ segsort_kernel(const typename KeyOf<KB>::type* __restrict__ in, typename KeyOf<K
 
   const size_t seg_bytes = (size_t)seg_len * KB;
   for (unsigned long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
-    if (ld_relaxed(&ctrl->abort)) return;
+    // one thread reads the abort flag; its answer reaches the others through the barrier below,
+    // so the whole CTA leaves together
+    int stop = 0;
+    if (tid == 0) stop = (int)ld_relaxed(&ctrl->abort);
     const K* src = in + seg * seg_len;
     const bool use_bulk = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && (seg_bytes % 16 == 0);
     if (use_bulk) {
       for (unsigned int e = seg_len + tid; e < TILE; e += THREADS) skeys[e] = pad;
       int arrived = 1;
-      if (tid == 0) {
+      if (tid == 0 && !stop) {
         fence_proxy_async();  // earlier generic accesses to the buffer are ordered before the copy
         mbar_expect_tx(bar, (uint32_t)seg_bytes);
         bulk_load(skeys, src, (uint32_t)seg_bytes, bar);
         arrived = mbar_wait_bounded(bar, phase);  // one thread waits; the others park at the barrier
       }
       phase ^= 1u;
-      if (!__syncthreads_and(arrived)) {
-        if (tid == 0) raise_timeout(ctrl);
+      if (!__syncthreads_and(arrived && !stop)) {
+        if (tid == 0 && !stop) raise_timeout(ctrl);
         return;
       }
     } else {
       for (unsigned int e = tid; e < TILE; e += THREADS) skeys[e] = e < seg_len ? src[e] : pad;
-      __syncthreads();
+      if (__syncthreads_or(stop)) return;
     }
 
     K key[ITEMS];

@@ -17,6 +17,7 @@ from . import _lib
 class Runtime:
     def __init__(self) -> None:
         self._ws: dict[int, torch.Tensor] = {}
+        self._sticky: dict[int, torch.Tensor] = {}
         self._comm = None
 
     # --- topology -------------------------------------------------------------------------
@@ -57,6 +58,29 @@ class Runtime:
 
     def release_workspace(self) -> None:
         self._ws.clear()
+
+    # --- device-side status of the sorts enqueued so far ------------------------------------
+    def note_sort(self, ws: torch.Tensor) -> None:
+        """Folds the status word at the head of a workspace (0, or the code a kernel left when a
+        bounded wait ran out) into a per-device word that survives the workspace's reuse.  Stream
+        ordered, no synchronisation."""
+        dev = torch.cuda.current_device()
+        acc = self._sticky.get(dev)
+        if acc is None:
+            acc = self._sticky[dev] = torch.zeros(1, dtype=torch.int32, device=self.device)
+        torch.maximum(acc, ws[:4].view(torch.int32), out=acc)
+
+    def raise_pending(self) -> None:
+        """Called where a result reaches the host: raises if any sort since the last call reported
+        a device-side failure (role of CUPYNUMERIC_CHECK_CUDA_STREAM in the reference's task
+        bodies, ``src/cupynumeric/cuda_help.h:291-302``)."""
+        acc = self._sticky.get(torch.cuda.current_device()) if torch.cuda.is_available() else None
+        if acc is None:
+            return
+        status = int(acc.item())
+        if status != 0:
+            acc.zero_()
+            raise _lib.B2SError(status, "a sort kernel")
 
 
 runtime = Runtime()

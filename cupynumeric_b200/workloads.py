@@ -99,3 +99,101 @@ def _apply_swaps(a: np.ndarray, ii: np.ndarray, jj: np.ndarray) -> None:
             for i, j in zip(bi.tolist(), bj.tolist()):
                 a[i], a[j] = a[j], a[i]
         pos = end
+
+
+# ------------------------------------------------------------------------------------------------
+# The same five distributions drawn on the GPU with torch's seeded generator: the full-size
+# benchmark configurations (2^28 keys per GPU) take minutes to draw with NumPy on the host and a
+# second on the device.  Same shapes, sizes and value distributions; a different random stream.
+# ------------------------------------------------------------------------------------------------
+def _gen(device, seed: int):
+    import torch
+
+    g = torch.Generator(device=device)
+    g.manual_seed(int(seed))
+    return g
+
+
+def c1_int32_uniform_device(n: int, device, seed: int = 101):
+    import torch
+
+    return torch.randint(-2**31, 2**31, (n,), dtype=torch.int64, device=device, generator=_gen(device, seed)).to(torch.int32)
+
+
+def c2_float32_nan_dups_device(n: int, device, seed: int = 202):
+    import torch
+
+    g = _gen(device, seed)
+    a = torch.randn(n, dtype=torch.float32, device=device, generator=g)
+    k = n // 100
+    if k:
+        dst = torch.randint(0, n, (k,), device=device, generator=g)
+        src = torch.randint(0, n, (k,), device=device, generator=g)
+        a[dst] = a[src]
+    k = n // 1000
+    if k:
+        a[torch.randint(0, n, (k,), device=device, generator=g)] = float("nan")
+    return a
+
+
+def c3_float64_rows_device(shape, device, seed: int = 303):
+    import torch
+
+    return torch.rand(shape, dtype=torch.float64, device=device, generator=_gen(device, seed))
+
+
+def c4_int64_zipf_shard_device(n: int, rank: int, device, seed: int = 404, a: float = 1.2):
+    """Zipf(a) by rejection from the continuous envelope (Devroye's method, the one NumPy uses),
+    clipped to [1, 2^40 - 1]."""
+    import torch
+
+    g = _gen(device, seed + rank)
+    am1, b = a - 1.0, 2.0 ** (a - 1.0)
+    out = torch.empty(n, dtype=torch.int64, device=device)
+    chunk = 1 << 24
+    for lo in range(0, n, chunk):
+        m = min(chunk, n - lo)
+        part = torch.empty(m, dtype=torch.float64, device=device)
+        todo = torch.arange(m, device=device)
+        while todo.numel():
+            u = 1.0 - torch.rand(todo.numel(), dtype=torch.float64, device=device, generator=g)
+            v = torch.rand(todo.numel(), dtype=torch.float64, device=device, generator=g)
+            x = torch.floor(u ** (-1.0 / am1))
+            tm1 = torch.expm1(am1 * torch.log1p(1.0 / x))            # T - 1, T = (1 + 1/x)^(a-1)
+            ok = (x >= 1) & (v * x * tm1 / (b - 1.0) <= (tm1 + 1.0) / b)
+            part[todo[ok]] = x[ok]
+            todo = todo[~ok]
+        out[lo:lo + m] = torch.clamp(part, max=float(2**40 - 1)).to(torch.int64)
+    return out
+
+
+def c5_uint64_nearly_sorted_shard_device(n_per_rank: int, rank: int, nranks: int, device, seed: int = 505):
+    """This rank's range of the ascending array 0..N-1 (N = n_per_rank * nranks) after N/100
+    random pair swaps.  Every rank draws the same pair list; pairs that share a position with
+    another pair are dropped, which makes the result independent of the order of application
+    (and so identical on every rank) and keeps the global array a permutation of 0..N-1.
+    Returned as int64 bit patterns of the uint64 keys (all values are below 2^63)."""
+    import torch
+
+    n = n_per_rank * nranks
+    g = _gen(device, seed)
+    k = n // 100
+    ii = torch.randint(0, n, (k,), device=device, generator=g)
+    jj = torch.randint(0, n, (k,), device=device, generator=g)
+    both = torch.cat([ii, jj])
+    order = torch.argsort(both)
+    s = both[order]
+    dup = torch.zeros(2 * k, dtype=torch.bool, device=device)
+    if k:
+        same = s[1:] == s[:-1]
+        dup[order[1:][same]] = True
+        dup[order[:-1][same]] = True
+    keep = ~(dup[:k] | dup[k:])
+    ii, jj = ii[keep], jj[keep]
+    lo, hi = rank * n_per_rank, (rank + 1) * n_per_rank
+    a = torch.arange(lo, hi, dtype=torch.int64, device=device)
+    mi = (ii >= lo) & (ii < hi)
+    a[ii[mi] - lo] = jj[mi]
+    mj = (jj >= lo) & (jj < hi)
+    a[jj[mj] - lo] = ii[mj]
+    return a

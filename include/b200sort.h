@@ -106,11 +106,15 @@ int b2s_check_status(void* ws, void* cuda_stream);
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
  * that first call before any stream capture begins.  All calls on a device share the one array:
  * two calls whose kernels may overlap on the GPU (different streams, no ordering) race with each
- * other; calls on one stream are safe.  A device-side wait that ran out cannot be read back
- * through b2s_check_status here. */
+ * other; calls on one stream are safe.  A device-side wait that ran out is read back with
+ * b2s_noalloc_check_status (the status word lives in the same array, so it reports the last call
+ * made on the current device). */
 #define B2S_NOALLOC_SCRATCH_BYTES (32u << 20)
 int b2s_local_sort_noalloc(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t volume,
                            size_t segment, int64_t index_offset, int ndim_is_1, void* cuda_stream);
+/* b2s_check_status for the fixed scratch of b2s_local_sort_noalloc on the current device.  Like
+ * that entry point it allocates nothing and has no counterpart in the reference. */
+int b2s_noalloc_check_status(void* cuda_stream);
 
 /* ---- distributed 1-D sort ------------------------------------------------------------------- */
 

@@ -1,10 +1,10 @@
 """Micro-benchmarks of single kernels through the C ABI, with CUDA-event timing per kernel family.
 
-    python -m cupynumeric_b200.kernel_bench merge --dtype int64 --runs 8 --log2 27 [--payload]
-    python -m cupynumeric_b200.kernel_bench sort  --dtype float32 --log2 28 [--argsort] [--segment L]
+    python kernel_bench.py merge --dtype int64 --runs 8 --log2 27 [--payload]
+    python kernel_bench.py sort  --dtype float32 --log2 28 [--argsort] [--segment L]
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
-        -m cupynumeric_b200.kernel_bench dist --dtype float32 --log2 27 [--argsort]
+        kernel_bench.py dist --dtype float32 --log2 27 [--argsort]
 
 `merge` times b2s_kway_merge on `runs` sorted runs holding 2^log2 elements in all; `sort` times
 b2s_local_sort; `dist` (one process per GPU) times the distributed 1-D sort of 2^log2 keys per GPU,
@@ -20,8 +20,13 @@ import ctypes
 import numpy as np
 import torch
 
-from . import _lib
-from ._thunk._sort import local_sort_tile
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from cupynumeric_b200 import _lib  # noqa: E402
+from cupynumeric_b200._thunk._sort import local_sort_tile  # noqa: E402
 
 KINDS = ["hist", "scan", "sweep", "fixup", "segsort", "unit", "dist", "merge", "xchg"]
 
@@ -104,8 +109,8 @@ def bench_dist(args) -> None:
 
     import torch.distributed as dist
 
-    from . import array, argsort, sort
-    from ._dist import destroy_comm
+    from cupynumeric_b200 import array, argsort, sort
+    from cupynumeric_b200._dist import destroy_comm
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))

@@ -18,4 +18,4 @@ Both are pinned against the golden vectors of the reference's C++ tests
 has no test with NaN input; the contract used here is NumPy's NaN-last order.
 """
 from .np_oracle import np_sort, np_argsort, np_task_sort, complex_lex_argsort  # noqa: F401
-from .thrust_oracle import thrust_task_sort, num_threads, build as build_thrust_oracle  # noqa: F401
+from .thrust_oracle import thrust_task_sort, num_threads, set_num_threads, build as build_thrust_oracle  # noqa: F401

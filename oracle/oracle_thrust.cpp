@@ -188,3 +188,6 @@ int oracle_thrust_version(void) { return THRUST_VERSION; }
 
 #include <omp.h>
 extern "C" int oracle_num_threads(void) { return omp_get_max_threads(); }
+// Threads of the OpenMP back-end from now on (launchers such as torch.distributed.run export
+// OMP_NUM_THREADS=1 to their children; the benchmark's reference arm undoes that here).
+extern "C" void oracle_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }

@@ -43,6 +43,14 @@ def _load():
     return _lib
 
 
+def set_num_threads(n: int) -> None:
+    """Sets the thread count of the OpenMP back-end for later calls."""
+    lib = _load()
+    lib.oracle_set_num_threads.argtypes = [ctypes.c_int]
+    lib.oracle_set_num_threads.restype = None
+    lib.oracle_set_num_threads(int(n))
+
+
 def num_threads() -> int:
     """Threads the OpenMP back-end will use (OMP_NUM_THREADS or all cores)."""
     return int(_load().oracle_num_threads())

@@ -81,6 +81,7 @@ def main():
         parts = [None] * world
         dist.all_gather_object(parts, flat.to_numpy())
         assert np.array_equal(np.concatenate(parts), np.sort(whole, axis=None, kind="stable")), "flattened sort"
+        assert flat.global_lo == sum(len(p) for p in parts[:rank]), "global start of the flattened part"
         rows = num.sort(arr, axis=1).to_numpy()
         assert np.array_equal(rows, np.sort(block, axis=1))
         dist.barrier()

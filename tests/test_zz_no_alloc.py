@@ -25,6 +25,8 @@ def noalloc_sort(keys: np.ndarray, segment: int, argsort: bool, index_offset: in
                                     d_idx.data_ptr() if argsort else None, keys.size, segment, index_offset,
                                     int(ndim_is_1), torch.cuda.current_stream().cuda_stream)
     _lib.check(st, "b2s_local_sort_noalloc")
+    # no wait inside the kernels ran out: the status word of the library-held scratch reads 0
+    _lib.check(lib.b2s_noalloc_check_status(torch.cuda.current_stream().cuda_stream), "b2s_noalloc_check_status")
     torch.cuda.synchronize()
     return to_host(d_out, keys.dtype), (d_idx.cpu().numpy() if argsort else None)
 
