@@ -77,7 +77,14 @@ FREE_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p)
 BARRIER_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p)
 
 # layout of one sample record (see include/b200sort.h)
-SAMPLE_DTYPE = np.dtype([("okey", np.uint64), ("pos", np.int64), ("rank", np.int32), ("valid", np.int32)])
+SAMPLE_DTYPE = np.dtype([("okey", np.uint64), ("okey_lo", np.uint64), ("pos", np.int64), ("weight", np.int64),
+                         ("rank", np.int32), ("pad", np.int32)])
+
+
+class CommOps(ctypes.Structure):
+    """b2s_comm_ops: the collectives table of the distributed calls."""
+    _fields_ = [("ctx", ctypes.c_void_p), ("all_gather", ctypes.c_void_p), ("barrier", ctypes.c_void_p),
+                ("exchange", ctypes.c_void_p)]
 
 _lib = None
 
@@ -94,7 +101,14 @@ SIGNATURES = {
     "b2s_noalloc_check_status": (_I, [_P]),
     "b2s_dist_sort_1d": (_I, [_I, _P, _SZ, _I64, _I, _P, _I, _I, _P, _P, _P, _P, _P,
                                ctypes.POINTER(_P), ctypes.POINTER(_SZ), ctypes.POINTER(_I64), _P]),
+    "b2s_dist_sort_1d_ops": (_I, [_I, _P, _SZ, _I64, _I, _P, _I, _I, _P, _P, _P, _P, _P,
+                                   ctypes.POINTER(_P), ctypes.POINTER(_SZ), ctypes.POINTER(_I64), _P]),
     "b2s_dist_rebalance_1d": (_I, [_SZ, _P, _SZ, _I64, _P, _SZ, _I64, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "b2s_dist_rebalance_1d_ops": (_I, [_SZ, _P, _SZ, _I64, _P, _SZ, _I64, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "b2s_nccl_comm_ops": (_I, [_P, _P, _I, _I, _P]),
+    "b2s_nccl_comm_ops_release": (None, [_P]),
+    "b2s_thread_comm_create": (_I, [_I, _P]),
+    "b2s_thread_comm_destroy": (None, [_P]),
     "b2s_kway_merge_workspace_bytes": (_I, [_SZ, _I, ctypes.POINTER(_SZ)]),
     "b2s_kway_merge": (_I, [_I, _I, _P, _P, _P, _P, _P, _SZ, _P]),
     "b2s_nccl_unique_id": (_I, [_P]),
@@ -102,9 +116,10 @@ SIGNATURES = {
     "b2s_nccl_comm_destroy": (_I, [_P]),
     "b2s_samples_per_rank": (_I, []),
     "b2s_host_sample_position": (ctypes.c_longlong, [ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
+    "b2s_host_sample_weight": (ctypes.c_longlong, [ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
     "b2s_host_sort_samples": (None, [_P, _SZ]),
     "b2s_host_select_splitters": (_I, [_P, _SZ, _I, _P]),
-    "b2s_host_cut_position": (ctypes.c_longlong, [_P, _I, ctypes.c_longlong, ctypes.c_longlong]),
+    "b2s_host_bucket_of": (_I, [_P, _I, _I, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_longlong]),
     "b2s_searchsorted": (_I, [_I, _P, _SZ, _I64, _P, _SZ, _I, _P, _P]),
     "b2s_unique_workspace_bytes": (_I, [_SZ, ctypes.POINTER(_SZ)]),
     "b2s_unique_sorted": (_I, [_I, _P, _SZ, _P, ctypes.POINTER(_SZ), _P, _SZ, _P]),

@@ -43,13 +43,14 @@ inline size_t radix_ws(int kb, size_t n, bool pairs)
 }
 
 inline cudaError_t radix_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int n,
-                             int64_t off, unsigned char* ws, cudaStream_t s, int idx32 = 0)
+                             int64_t off, unsigned char* ws, cudaStream_t s, int idx32 = 0,
+                             const uint32_t* idx_in = nullptr)
 {
   switch (kb) {
-    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s, idx32);
-    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s, idx32);
-    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s, idx32);
-    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s, idx32);
+    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
+    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
+    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
+    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
   }
 }
 
@@ -143,23 +144,25 @@ inline int chunk_layout(int dtype, int kb, size_t n, bool argsort, ChunkLayout* 
 }
 
 
-// Stable 1-D argsort that leaves 32-bit positions 0..n-1 instead of int64 global indices: the
-// distributed sort ships these through the exchange (4 bytes per element instead of 8) and adds
-// the source rank's offset after the merge.  Only for sizes the single radix sort takes.
+// Sizes the single radix sort takes with 32-bit payloads carried through its passes.
 bool local_sort_pos32_supported(size_t n) { return n > SEG_CAP && n < single_sort_limit(); }
 
-int local_sort_pos32(int dtype, const void* keys_in, void* keys_out, uint32_t* pos_out, size_t n, void* ws,
-                     size_t ws_bytes, cudaStream_t stream)
+// Stable 1-D argsort of keys that already carry a 32-bit payload each (pay_in[i] belongs to
+// keys_in[i]): idx_out[k] = index_offset + payload of the k-th smallest key.  The distributed sort
+// uses it on what a rank received: the payload is the element's global position minus a common
+// base, and travelling as 32 bits it costs the radix passes no more than a plain argsort.
+int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
+                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream)
 {
   DtypeInfo di;
   if (!dtype_info(dtype, &di) || !local_sort_pos32_supported(n)) return B2S_ERR_UNSUPPORTED;
-  if (keys_in == nullptr || keys_out == nullptr || pos_out == nullptr) return B2S_ERR_INVALID_ARG;
+  if (keys_in == nullptr || pay_in == nullptr || idx_out == nullptr) return B2S_ERR_INVALID_ARG;
   size_t need = 0;
   int rc      = b2s_workspace_bytes(dtype, n, n, 1, &need);
   if (rc != B2S_OK) return rc;
   if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
-  const cudaError_t e = radix_any(di.kb, di.xf, keys_in, keys_out, reinterpret_cast<int64_t*>(pos_out), (unsigned int)n, 0,
-                                  static_cast<unsigned char*>(ws), stream, 1);
+  const cudaError_t e = radix_any(di.kb, di.xf, keys_in, nullptr, idx_out, (unsigned int)n, index_offset,
+                                  static_cast<unsigned char*>(ws), stream, 0, pay_in);
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 

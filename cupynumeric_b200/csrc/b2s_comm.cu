@@ -151,7 +151,6 @@ int b2s_nccl_comm_ops(b2s_comm_ops* ops, void* nccl_comm, int rank, int nranks, 
   ops->all_gather = nccl_all_gather;
   ops->barrier    = nccl_barrier;
   ops->exchange   = nccl_exchange;
-  ops->same_process = 0;
   return B2S_OK;
 }
 
@@ -171,7 +170,6 @@ int b2s_thread_comm_create(int nranks, b2s_comm_ops* ops_out)
     ops_out[r].all_gather   = thread_all_gather;
     ops_out[r].barrier      = thread_barrier;
     ops_out[r].exchange     = thread_exchange;
-    ops_out[r].same_process = 1;
   }
   return B2S_OK;
 }

@@ -126,8 +126,9 @@ struct FixDesc {
   const void* copy_src;  // non-null: copy copy_bytes from here to copy_dst
   void* copy_dst;
   unsigned long long copy_bytes;
-  int64_t* synth_idx;    // non-null: write index_offset + i
+  int64_t* synth_idx;    // non-null: write index_offset + i (or + widen_src[i])
   uint32_t* synth_idx32; // non-null: write i
+  const uint32_t* widen_src;  // with synth_idx: the caller's 32-bit payload takes the place of i
 };
 
 struct Ctrl {

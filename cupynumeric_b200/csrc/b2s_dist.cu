@@ -1,8 +1,16 @@
-// Distributed 1-D sort over the GPUs of one NVSwitch box: local sort -> regular oversampling ->
-// NCCL all-gather of samples -> splitters -> cut positions -> NCCL all-gather of counts ->
-// one grouped send/recv exchange of keys (and indices) -> stable k-way merge.
-// Replaces sample_sort_nccl_nd for 1-D arrays (src/cupynumeric/sort/sort.cu:1270-1784) and the
-// surrounding buffer handling of SortImplBody<GPU> (sort.cu:1797-1940).
+// Distributed 1-D sort over the GPUs of one NVSwitch box, as a partition-first sample sort:
+//   samples of the unsorted tile -> all-gather -> weighted splitters (on the device) ->
+//   every element is classified by (key, rank, position) and written straight into the receive
+//   buffer of its destination GPU by the partition kernel (plain stores over NVLink) ->
+//   one barrier -> each GPU sorts what it received with the local radix sort.
+// The runs a GPU receives lie in source-rank order and keep their input order, so the stable
+// local sort of their concatenation is the global stable sort; no merge is needed.
+// Replaces sample_sort_nccl_nd for 1-D arrays (src/cupynumeric/sort/sort.cu:1270-1784), which
+// sorts first, exchanges through NCCL and merges in log2(P) sweeps, and the surrounding buffer
+// handling of SortImplBody<GPU> (sort.cu:1797-1940).
+//
+// Also here: the stable k-way merge entry point (used by local sorts of 2^30 keys and more) and
+// the move of variable-length parts into fixed extents (rebalance).
 #include <nccl.h>
 
 #include <algorithm>
@@ -10,6 +18,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <type_traits>
 #include <vector>
 
@@ -20,8 +29,8 @@
 namespace b2s {
 // defined with the local sort
 bool local_sort_pos32_supported(size_t n);
-int local_sort_pos32(int dtype, const void* keys_in, void* keys_out, uint32_t* pos_out, size_t n, void* ws,
-                     size_t ws_bytes, cudaStream_t stream);
+int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
+                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream);
 }  // namespace b2s
 #include "b2s_dist_host.h"
 #include "b2s_merge.cuh"
@@ -45,57 +54,343 @@ static int kb_of(int dtype, int* xf)
     case B2S_UINT64: *xf = XF_UNSIGNED; return 8;
     case B2S_FLOAT64: *xf = XF_FLOAT; return 8;
     case B2S_COMPLEX64: *xf = XF_CFLOAT; return 8;
+    case B2S_COMPLEX128: *xf = XF_CFLOAT; return 16;  // (real, imaginary) doubles: a two-word key
     default: return 0;
   }
 }
 
-// Regular samples of the locally sorted keys, as (ordered key, rank, position) triples.
+// ---------------------------------------------------------------------------------------------
+// Keys as the partition kernels see them: raw storage type and two-word ordered image.
+// ---------------------------------------------------------------------------------------------
+template <int KB> struct DKey {
+  using Raw = typename KeyOf<KB>::type;
+  static __device__ __forceinline__ OKey okey(Raw r, int xf) { return OKey{(unsigned long long)to_ordered_rt<KB>(r, xf), 0ull}; }
+};
+template <> struct DKey<16> {
+  using Raw = ulonglong2;  // x: bits of the real part, y: bits of the imaginary part
+  static __device__ __forceinline__ OKey okey(Raw r, int)
+  {
+    return OKey{to_ordered<8, XF_FLOAT>(r.x), to_ordered<8, XF_FLOAT>(r.y)};
+  }
+};
+
+// What every rank contributes to the first all-gather.
+struct BlockA {
+  long long n_local;
+  long long global_offset;
+  long long status;        // a b2s_status_t: this rank's failure so far
+  long long capacity;      // elements its receive buffers hold
+  long long reserved[4];
+  PeerRecord rec;          // where the others can write (receive keys, receive payload)
+  OKey okey[SAMPLES_PER_RANK];
+};
+
+// ... and to the second one.
+struct BlockB {
+  long long status;
+  long long mapped;                 // 1: this rank can write into every rank's receive buffers
+  long long total[MAX_BUCKETS];     // elements of my tile per destination
+  long long reserved[6];
+};
+
+// Regular samples of the unsorted tile: ordered keys only; rank, position and weight follow
+// from the slot number and the tile size (sample_position / sample_weight).
 template <int KB>
-__global__ void sample_kernel(const void* sorted, long long n, int s, int rank, int xf, Sample* out)
+__global__ void sample_kernel(const typename DKey<KB>::Raw* __restrict__ keys, long long n, int xf, OKey* __restrict__ out)
 {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= s) return;
-  Sample sm;
-  const long long s_eff = n < s ? n : s;
-  if (j < s_eff) {
-    const long long p = sample_position(j, s_eff, n);
-    sm.okey  = okey_at<KB>(sorted, p, xf);
-    sm.pos   = p;
-    sm.rank  = rank;
-    sm.valid = 1;
-  } else {
-    sm.okey = ~0ull;
-    sm.pos = 0;
-    sm.rank = rank;
-    sm.valid = 0;
-  }
-  out[j] = sm;
+  if (j >= SAMPLES_PER_RANK) return;
+  const long long s_eff = n < SAMPLES_PER_RANK ? n : SAMPLES_PER_RANK;
+  out[j] = j < s_eff ? DKey<KB>::okey(keys[sample_position(j, s_eff, n)], xf) : OKey{~0ull, ~0ull};
 }
 
-// cuts[k] for k = 1..nranks-1: how many of my sorted elements go to ranks < k.
-template <int KB>
-__global__ void cut_kernel(const void* sorted, long long n, const Sample* splitters, int nranks, int rank,
-                           int xf, long long* cuts, long long tag0, long long tag1, long long tag2)
+// Gathered blocks -> one Sample per slot (rank-major, positions ascending inside a rank, which
+// is the triple order among equal keys) and the two words the samples are ordered by.
+__global__ void build_samples_kernel(const BlockA* __restrict__ blocks, int nranks, Sample* __restrict__ samples,
+                                     unsigned long long* __restrict__ key_hi, unsigned long long* __restrict__ key_lo)
 {
-  const int k = blockIdx.x * blockDim.x + threadIdx.x + 1;
-  if (k >= nranks) return;
-  const Sample sp = splitters[k - 1];
-  long long c;
-  if (!sp.valid) {
-    c = n;  // no populated sample anywhere right of this splitter
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= nranks * SAMPLES_PER_RANK) return;
+  const int r = t / SAMPLES_PER_RANK, j = t % SAMPLES_PER_RANK;
+  const long long n = blocks[r].n_local;
+  const long long s_eff = n < SAMPLES_PER_RANK ? n : SAMPLES_PER_RANK;
+  Sample s;
+  s.rank = r;
+  s.pad_ = 0;
+  if (j < s_eff) {
+    s.okey   = blocks[r].okey[j];
+    s.pos    = sample_position(j, s_eff, n);
+    s.weight = sample_weight(j, s_eff, n);
   } else {
-    const long long lower = lower_bound_okey<KB>(sorted, 0, n, sp.okey, xf);
-    const long long upper = sp.okey == ~0ull ? n : lower_bound_okey<KB>(sorted, lower, n, sp.okey + 1, xf);
-    c = cut_position(sp, rank, lower, upper);
+    s.okey   = OKey{~0ull, ~0ull};
+    s.pos    = 0;
+    s.weight = 0;
   }
-  cuts[k] = c;
-  if (k == 1) {
-    cuts[0]          = 0;
-    cuts[nranks]     = n;
-    cuts[nranks + 1] = tag0;  // three words that travel with the cuts to every rank
-    cuts[nranks + 2] = tag1;
-    cuts[nranks + 3] = tag2;
+  samples[t] = s;
+  key_hi[t]  = s.okey.hi;
+  key_lo[t]  = s.okey.lo;
+}
+
+// out[i] = in[order[i]]
+__global__ void gather_u64_kernel(const unsigned long long* __restrict__ in, const int64_t* __restrict__ order, int n,
+                                  unsigned long long* __restrict__ out)
+{
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = in[order[i]];
+}
+// out[i] = first[second[i]]
+__global__ void compose_kernel(const int64_t* __restrict__ first, const int64_t* __restrict__ second, int n, int64_t* __restrict__ out)
+{
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = first[second[i]];
+}
+
+// One CTA: cumulative weights along the ordered samples, then splitter k = the first sample whose
+// inclusive cumulative weight reaches splitter_target(k); written in global form (all ranks get
+// the same) and localised for `my_rank`.  `cum` is scratch for `count` values.
+constexpr int SELECT_THREADS = 1024;
+__global__ void __launch_bounds__(SELECT_THREADS)
+select_splitters_kernel(const Sample* __restrict__ samples, const int64_t* __restrict__ order, int count, int nb, int my_rank,
+                        long long* __restrict__ cum, Sample* __restrict__ splitters, LocalSplitter* __restrict__ local, int nlocal)
+{
+  __shared__ long long part[SELECT_THREADS];
+  const int tid = threadIdx.x;
+  const int per = (count + SELECT_THREADS - 1) / SELECT_THREADS;
+  const int lo = min(tid * per, count), hi = min(lo + per, count);
+  long long sum = 0;
+  for (int t = lo; t < hi; ++t) sum += samples[order[t]].weight;
+  part[tid] = sum;
+  __syncthreads();
+  for (int o = 1; o < SELECT_THREADS; o <<= 1) {
+    const long long v = tid >= o ? part[tid - o] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
   }
+  long long run = part[tid] - sum;
+  for (int t = lo; t < hi; ++t) {
+    run += samples[order[t]].weight;
+    cum[t] = run;
+  }
+  const long long total = part[SELECT_THREADS - 1];
+  __syncthreads();  // cum[] was written by this CTA only: visible to all of its threads now
+  if (tid < nlocal) {
+    Sample sp{};
+    sp.okey = OKey{~0ull, ~0ull};
+    if (tid < nb - 1 && total > 0) {
+      const long long target = splitter_target(tid + 1, total, nb);
+      int a = 0, b = count;  // first t with cum[t] >= target
+      while (a < b) {
+        const int m = (a + b) >> 1;
+        if (cum[m] < target) a = m + 1; else b = m;
+      }
+      if (a < count) sp = samples[order[a]];
+    }
+    if (tid < nb - 1) splitters[tid] = sp;
+    local[tid] = localise(sp, my_rank);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The partition of a tile: a counting pass, a scan over tiles, a scatter pass.
+// ---------------------------------------------------------------------------------------------
+constexpr int PART_THREADS = 256;
+constexpr int PART_ITEMS   = 16;
+constexpr int PART_TILE    = PART_THREADS * PART_ITEMS;
+constexpr int PART_WARPS   = PART_THREADS / 32;
+constexpr unsigned int NO_BUCKET = 0xFFu;
+
+// Destination of an element of the tile; `nsplit` = padded bucket count - 1 (padding splitters
+// are invalid, nothing lies right of them), so the search takes the same steps for every lane.
+__device__ __forceinline__ unsigned int classify(const LocalSplitter* split, int nsplit, const OKey& k, long long pos)
+{
+  return (unsigned int)bucket_of(split, nsplit, k, pos);
+}
+
+template <int KB>
+__global__ void __launch_bounds__(PART_THREADS)
+part_count_kernel(const typename DKey<KB>::Raw* __restrict__ keys, long long n, int xf, const LocalSplitter* __restrict__ split,
+                  int nbp, unsigned int* __restrict__ tile_counts)
+{
+  __shared__ LocalSplitter ssplit[MAX_BUCKETS];
+  __shared__ unsigned int cnt[MAX_BUCKETS];
+  const int tid = threadIdx.x, lane = tid & 31;
+  if (tid < nbp - 1) ssplit[tid] = split[tid];
+  if (tid < MAX_BUCKETS) cnt[tid] = 0;
+  __syncthreads();
+  const long long base = (long long)blockIdx.x * PART_TILE;
+#pragma unroll 4
+  for (int i = 0; i < PART_ITEMS; ++i) {
+    const long long e = base + (long long)i * PART_THREADS + tid;
+    unsigned int b    = NO_BUCKET;
+    if (e < n) b = classify(ssplit, nbp - 1, DKey<KB>::okey(keys[e], xf), e);
+    const unsigned int peers = __match_any_sync(0xFFFFFFFFu, b);
+    if (b != NO_BUCKET && lane == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned int)__popc(peers));
+  }
+  __syncthreads();
+  if (tid < nbp) tile_counts[(size_t)blockIdx.x * nbp + tid] = cnt[tid];
+}
+
+// Bucket b = blockIdx.x: exclusive prefix of its per-tile counts over the tiles, and its total.
+constexpr int SCAN_THREADS = 1024;
+__global__ void __launch_bounds__(SCAN_THREADS)
+tile_scan_kernel(const unsigned int* __restrict__ tile_counts, long long ntiles, int nbp, unsigned long long* __restrict__ tile_off,
+                 long long* __restrict__ totals)
+{
+  __shared__ unsigned long long part[SCAN_THREADS];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const long long per = (ntiles + SCAN_THREADS - 1) / SCAN_THREADS;
+  const long long lo = min((long long)tid * per, ntiles), hi = min(lo + per, ntiles);
+  unsigned long long sum = 0;
+  for (long long t = lo; t < hi; ++t) sum += tile_counts[t * nbp + b];
+  part[tid] = sum;
+  __syncthreads();
+  for (int o = 1; o < SCAN_THREADS; o <<= 1) {
+    const unsigned long long v = tid >= o ? part[tid - o] : 0;
+    __syncthreads();
+    part[tid] += v;
+    __syncthreads();
+  }
+  unsigned long long run = part[tid] - sum;
+  for (long long t = lo; t < hi; ++t) {
+    tile_off[t * nbp + b] = run;
+    run += tile_counts[t * nbp + b];
+  }
+  if (tid == SCAN_THREADS - 1) totals[b] = (long long)part[tid];
+}
+
+// Where the elements of each bucket go: the destination rank's receive buffers, already advanced
+// to the start of this rank's run in them.
+struct PartDst {
+  void* keys[MAX_BUCKETS];
+  void* pay[MAX_BUCKETS];
+};
+
+template <int KB, int PAYB> struct PartSmem {
+  static constexpr size_t KEY_BYTES = (size_t)PART_TILE * KB;
+  static constexpr size_t OFF_PAY   = KEY_BYTES;
+  static constexpr size_t OFF_SPLIT = OFF_PAY + (size_t)PART_TILE * PAYB;
+  static constexpr size_t OFF_WCNT  = OFF_SPLIT + sizeof(LocalSplitter) * MAX_BUCKETS;
+  static constexpr size_t OFF_START = OFF_WCNT + (size_t)PART_WARPS * MAX_BUCKETS * 4;  // MAX_BUCKETS + 1 entries
+  static constexpr size_t OFF_GOFF  = (OFF_START + (MAX_BUCKETS + 1) * 4 + 7) / 8 * 8;
+  static constexpr size_t OFF_DKEY  = OFF_GOFF + MAX_BUCKETS * 8;
+  static constexpr size_t OFF_DPAY  = OFF_DKEY + MAX_BUCKETS * 8;
+  static constexpr size_t BYTES     = OFF_DPAY + MAX_BUCKETS * 8;
+};
+
+// Stable partition of one tile: every element gets its rank among the tile's elements of the
+// same bucket (in input order), the tile is staged bucket by bucket in shared memory, and each
+// bucket's piece leaves as one contiguous, coalesced run - into this GPU's memory or, through a
+// peer mapping, another GPU's.  PAYB: 0 no payload, 4 the element's global position minus
+// `pay_base` as 32 bits, 8 its global position as int64.
+template <int KB, int PAYB>
+__global__ void __launch_bounds__(PART_THREADS)
+part_scatter_kernel(const typename DKey<KB>::Raw* __restrict__ keys, long long n, int xf, const LocalSplitter* __restrict__ split,
+                    int nbp, const unsigned long long* __restrict__ tile_off, const __grid_constant__ PartDst dst,
+                    long long global_offset, long long pay_base)
+{
+  using Raw = typename DKey<KB>::Raw;
+  using S   = PartSmem<KB, PAYB>;
+  extern __shared__ __align__(16) unsigned char smem[];
+  Raw* skeys                  = reinterpret_cast<Raw*>(smem);
+  unsigned char* spay         = smem + S::OFF_PAY;
+  LocalSplitter* ssplit       = reinterpret_cast<LocalSplitter*>(smem + S::OFF_SPLIT);
+  unsigned int* wcnt          = reinterpret_cast<unsigned int*>(smem + S::OFF_WCNT);
+  unsigned int* bstart        = reinterpret_cast<unsigned int*>(smem + S::OFF_START);
+  unsigned long long* goff    = reinterpret_cast<unsigned long long*>(smem + S::OFF_GOFF);
+  void** dkey                 = reinterpret_cast<void**>(smem + S::OFF_DKEY);
+  void** dpay                 = reinterpret_cast<void**>(smem + S::OFF_DPAY);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < nbp - 1) ssplit[tid] = split[tid];
+  if (tid < nbp) {
+    goff[tid] = tile_off[(size_t)blockIdx.x * nbp + tid];
+    dkey[tid] = dst.keys[tid];
+    dpay[tid] = dst.pay[tid];
+  }
+  for (int i = tid; i < PART_WARPS * MAX_BUCKETS; i += PART_THREADS) wcnt[i] = 0;
+  __syncthreads();
+
+  const long long base = (long long)blockIdx.x * PART_TILE;
+  const int valid      = (int)min((long long)PART_TILE, n - base);
+  // a warp owns PART_ITEMS * 32 consecutive elements; element i of lane l sits at 32 * i + l of them
+  const int stripe0 = warp * (PART_ITEMS * 32) + lane;
+  Raw key[PART_ITEMS];
+  unsigned int br[PART_ITEMS];  // bucket (bits 24..31) and rank among the warp's elements of that bucket
+  unsigned int* my_cnt  = wcnt + warp * MAX_BUCKETS;
+  const unsigned int lt = lanemask_lt();
+#pragma unroll
+  for (int i = 0; i < PART_ITEMS; ++i) {
+    const int e    = stripe0 + 32 * i;
+    unsigned int b = NO_BUCKET;
+    if (e < valid) {
+      key[i] = keys[base + e];
+      b      = classify(ssplit, nbp - 1, DKey<KB>::okey(key[i], xf), base + e);
+    }
+    const unsigned int peers = __match_any_sync(0xFFFFFFFFu, b);
+    unsigned int old         = 0;
+    if (b != NO_BUCKET) old = my_cnt[b];
+    __syncwarp();
+    if (b != NO_BUCKET) my_cnt[b] = old + __popc(peers);  // the same value from every lane of the group
+    __syncwarp();
+    br[i] = (b << 24) | (old + __popc(peers & lt));
+  }
+  __syncthreads();
+  // per bucket: exclusive prefix over the warps, then over the buckets (one warp)
+  if (tid < 32) {
+    unsigned int run = 0;
+    if (tid < nbp) {
+      for (int w = 0; w < PART_WARPS; ++w) {
+        const unsigned int t        = wcnt[w * MAX_BUCKETS + tid];
+        wcnt[w * MAX_BUCKETS + tid] = run;
+        run += t;
+      }
+    }
+    unsigned int incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    bstart[tid] = incl - run;
+    if (tid == 31) bstart[32] = incl;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < PART_ITEMS; ++i) {
+    const unsigned int b = br[i] >> 24;
+    if (b != NO_BUCKET) {
+      const unsigned int p = bstart[b] + my_cnt[b] + (br[i] & 0xFFFFFFu);
+      skeys[p]             = key[i];
+      const long long g    = global_offset + base + stripe0 + 32 * i;
+      if (PAYB == 4) reinterpret_cast<uint32_t*>(spay)[p] = (uint32_t)(g - pay_base);
+      if (PAYB == 8) reinterpret_cast<int64_t*>(spay)[p] = (int64_t)g;
+    }
+  }
+  __syncthreads();
+  // copy-out: staged position p belongs to the bucket whose range [bstart[b], bstart[b+1]) holds it
+  for (int p = tid; p < valid; p += PART_THREADS) {
+    int lo = 0, hi = nbp - 1;  // largest b with bstart[b] <= p
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (bstart[mid] <= (unsigned int)p) lo = mid; else hi = mid - 1;
+    }
+    const unsigned long long at = goff[lo] + (unsigned int)(p - bstart[lo]);
+    static_cast<Raw*>(dkey[lo])[at] = skeys[p];
+    if (PAYB == 4) static_cast<uint32_t*>(dpay[lo])[at] = reinterpret_cast<const uint32_t*>(spay)[p];
+    if (PAYB == 8) static_cast<int64_t*>(dpay[lo])[at] = reinterpret_cast<const int64_t*>(spay)[p];
+  }
+}
+
+// result[i] = payload[position[i]] (+ base for 32-bit payloads): turns an argsort of the receive
+// buffer into global indices when the radix passes could not carry the payload themselves.
+template <typename P>
+__global__ void gather_payload_kernel(const int64_t* __restrict__ position, const P* __restrict__ payload, long long n,
+                                      long long base, int64_t* __restrict__ result)
+{
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    result[i] = (int64_t)payload[position[i]] + base;
 }
 
 template <typename F>
@@ -108,7 +403,14 @@ static cudaError_t by_width(int kb, F&& f)
     default: return f(std::integral_constant<int, 8>{});
   }
 }
+template <typename F>
+static cudaError_t by_width16(int kb, F&& f)
+{
+  if (kb == 16) return f(std::integral_constant<int, 16>{});
+  return by_width(kb, f);
+}
 
+// Memory from the caller's allocator that goes back to it when the call ends, unless disowned.
 struct Scratch {
   b2s_alloc_fn alloc;
   b2s_free_fn release;
@@ -192,34 +494,16 @@ static int merge_runs(int kb, int xf, const MergeRuns& runs, long long total, bo
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 
-// Phases of the exchange/merge pipeline.
-#ifndef B2S_DIST_PHASES
-#define B2S_DIST_PHASES 2
-#endif
-constexpr int DIST_PHASES = B2S_DIST_PHASES;
-
-// One extra stream per device for the exchange, created on first use and kept.
-static cudaStream_t exchange_stream()
-{
-  static cudaStream_t streams[64] = {};
-  static std::mutex mu;  // two host threads may ask for the same device's stream together
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lock(mu);
-  if (streams[dev] == nullptr) {
-    if (cudaStreamCreateWithFlags(&streams[dev], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
-  }
-  return streams[dev];
-}
-
-// Host-side phase trace of the distributed sort (B2S_DIST_TRACE=1, rank 0 prints).
+// Host-side phase trace of the distributed sort (B2S_DIST_TRACE=1, rank 0 prints; "a": all ranks).
 struct PhaseTrace {
   bool on;
+  int rk;
   std::chrono::steady_clock::time_point t0;
   char line[512] = {0};
   int used = 0;
-  int rk = 0;
-  explicit PhaseTrace(int rank) : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank), t0(std::chrono::steady_clock::now()) {}
+  explicit PhaseTrace(int rank)
+    : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank),
+      t0(std::chrono::steady_clock::now()) {}
   void mark(const char* what)
   {
     if (!on) return;
@@ -234,24 +518,45 @@ struct PhaseTrace {
   ~PhaseTrace() { if (on) std::fprintf(stderr, "[b2s dist ms r%d]%s\n", rk, line); }
 };
 
-// CUDA events that are destroyed on every way out of the function that owns them
-struct Events {
-  std::vector<cudaEvent_t> ev;
-  cudaEvent_t make()
-  {
-    cudaEvent_t e = nullptr;
-    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-    ev.push_back(e);
-    return e;
-  }
-  ~Events()
-  {
-    for (cudaEvent_t e : ev) cudaEventDestroy(e);
-  }
+// One CUDA event that is destroyed on every way out of the function that owns it.
+struct Event {
+  cudaEvent_t ev = nullptr;
+  Event() { if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) ev = nullptr; }
+  ~Event() { if (ev) cudaEventDestroy(ev); }
 };
 
-#define CK_CUDA(x) do { if ((x) != cudaSuccess) return B2S_ERR_CUDA; } while (0)
-#define CK_NCCL(x) do { if ((x) != ncclSuccess) return B2S_ERR_NCCL; } while (0)
+// For rare failures inside the distributed calls: a local CUDA error is recorded and the rank
+// keeps taking part in every collective, so that no other rank is left waiting for it.
+struct Status {
+  int code = B2S_OK;
+  void cuda(cudaError_t e) { if (e != cudaSuccess && code == B2S_OK) code = B2S_ERR_CUDA; }
+  void set(int rc) { if (rc != B2S_OK && code == B2S_OK) code = rc; }
+  bool ok() const { return code == B2S_OK; }
+};
+
+// Used by the collectives of a rank whose control allocation failed: it has no memory of its own
+// to take part with, and taking part is what keeps the others from waiting for ever.  The contents
+// are never looked at (the rank's status says it failed).
+constexpr size_t EMERGENCY_BYTES = sizeof(BlockA) * (MAX_BUCKETS + 1);
+static __device__ __align__(256) unsigned char g_emergency[EMERGENCY_BYTES];
+
+static unsigned char* emergency_area()
+{
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_emergency) != cudaSuccess) return nullptr;
+  return static_cast<unsigned char*>(p);
+}
+
+static size_t single_limit()
+{
+  // the same rule as the local sort's (a testing aid lowers it)
+  const char* e = std::getenv("B2S_MAX_1D_LOG2");
+  if (e != nullptr) {
+    const int v = std::atoi(e);
+    if (v >= 10 && v <= 30) return (size_t)1 << v;
+  }
+  return (size_t)1 << 30;
+}
 
 }  // namespace b2s
 
@@ -259,39 +564,56 @@ using namespace b2s;
 
 extern "C" {
 
+// ---- host-side pieces, exported so that they can be exercised without a GPU -----------------
 void b2s_host_sort_samples(void* samples, size_t count)
 {
   Sample* s = static_cast<Sample*>(samples);
-  std::sort(s, s + count, [](const Sample& a, const Sample& b) { return sample_less(a, b); });
+  std::stable_sort(s, s + count, [](const Sample& a, const Sample& b) { return sample_less(a, b); });
 }
 
-int b2s_host_select_splitters(void* samples, size_t count, int nranks, void* splitters_out)
+int b2s_host_select_splitters(void* samples, size_t count, int nbuckets, void* splitters_out)
 {
-  if (samples == nullptr || splitters_out == nullptr || nranks < 1) return B2S_ERR_INVALID_ARG;
+  if (samples == nullptr || splitters_out == nullptr || nbuckets < 1 || nbuckets > MAX_BUCKETS) return B2S_ERR_INVALID_ARG;
   Sample* s   = static_cast<Sample*>(samples);
   Sample* out = static_cast<Sample*>(splitters_out);
   b2s_host_sort_samples(s, count);
-  long long populated = 0;
-  while ((size_t)populated < count && s[populated].valid) ++populated;
-  for (int k = 1; k < nranks; ++k) {
-    if (populated == 0) {
-      out[k - 1] = Sample{~0ull, 0, 0, 0};
-    } else {
-      out[k - 1] = s[splitter_index(k, populated, nranks)];
+  long long total = 0;
+  for (size_t t = 0; t < count; ++t) total += s[t].weight;
+  for (int k = 1; k < nbuckets; ++k) {
+    Sample sp{};
+    sp.okey = OKey{~0ull, ~0ull};
+    if (total > 0) {
+      const long long target = splitter_target(k, total, nbuckets);
+      long long run = 0;
+      for (size_t t = 0; t < count; ++t) {
+        run += s[t].weight;
+        if (run >= target) {
+          sp = s[t];
+          break;
+        }
+      }
     }
+    out[k - 1] = sp;
   }
   return B2S_OK;
 }
 
 long long b2s_host_sample_position(long long j, long long s, long long n) { return sample_position(j, s, n); }
+long long b2s_host_sample_weight(long long j, long long s, long long n) { return sample_weight(j, s, n); }
 
-long long b2s_host_cut_position(const void* splitter, int my_rank, long long lower, long long upper)
+int b2s_host_bucket_of(const void* splitters, int nsplit, int my_rank, unsigned long long okey_hi, unsigned long long okey_lo,
+                       long long pos)
 {
-  return cut_position(*static_cast<const Sample*>(splitter), my_rank, lower, upper);
+  if (nsplit < 0 || nsplit >= MAX_BUCKETS || (nsplit > 0 && splitters == nullptr)) return -1;
+  LocalSplitter local[MAX_BUCKETS];
+  const Sample* sp = static_cast<const Sample*>(splitters);
+  for (int k = 0; k < nsplit; ++k) local[k] = localise(sp[k], my_rank);
+  return bucket_of(local, nsplit, OKey{okey_hi, okey_lo}, pos);
 }
 
 int b2s_samples_per_rank(void) { return SAMPLES_PER_RANK; }
 
+// ---- k-way merge ---------------------------------------------------------------------------
 int b2s_kway_merge_workspace_bytes(size_t total, int nruns, size_t* bytes)
 {
   if (bytes == nullptr || nruns < 1 || nruns > MERGE_MAX_RUNS) return B2S_ERR_INVALID_ARG;
@@ -305,7 +627,7 @@ int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int6
 {
   int xf       = 0;
   const int kb = kb_of(dtype, &xf);
-  if (kb == 0) return B2S_ERR_UNSUPPORTED;
+  if (kb == 0 || kb == 16) return B2S_ERR_UNSUPPORTED;
   if (nruns < 1 || nruns > MERGE_MAX_RUNS || run_keys == nullptr || run_len == nullptr) return B2S_ERR_INVALID_ARG;
   MergeRuns runs{};
   runs.nruns      = nruns;
@@ -328,72 +650,12 @@ int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int6
                     static_cast<cudaStream_t>(cuda_stream));
 }
 
-int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
-                          void* out, size_t out_len, int64_t out_global_start, void* nccl_comm, int rank,
-                          int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
-                          b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
-{
-  if (elem_bytes == 0 || nranks < 1 || rank < 0 || rank >= nranks || alloc == nullptr) return B2S_ERR_INVALID_ARG;
-  if ((part_len > 0 && part == nullptr) || (out_len > 0 && out == nullptr)) return B2S_ERR_INVALID_ARG;
-  if (nranks > 1 && nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
-  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  ncclComm_t comm     = static_cast<ncclComm_t>(nccl_comm);
-  Scratch mem{alloc, release, alloc_ctx, {}};
-  // every rank learns where every rank's sorted part and output extent lie in the global order
-  long long mine[4] = {(long long)part_global_start, (long long)part_len, (long long)out_global_start, (long long)out_len};
-  std::vector<long long> all((size_t)4 * nranks);
-  if (nranks == 1) {
-    std::copy(mine, mine + 4, all.begin());
-  } else {
-    long long* d_all = static_cast<long long*>(mem.get(sizeof(long long) * 4 * (nranks + 1)));
-    if (d_all == nullptr) return B2S_ERR_WORKSPACE;
-    CK_CUDA(cudaMemcpyAsync(d_all + 4 * nranks, mine, sizeof(mine), cudaMemcpyHostToDevice, stream));
-    if (barrier) barrier(barrier_ctx);
-    CK_NCCL(ncclAllGather(d_all + 4 * nranks, d_all, sizeof(mine), ncclUint8, comm, stream));
-    if (barrier) barrier(barrier_ctx);
-    CK_CUDA(cudaMemcpyAsync(all.data(), d_all, sizeof(long long) * 4 * nranks, cudaMemcpyDeviceToHost, stream));
-    CK_CUDA(cudaStreamSynchronize(stream));
-  }
-  long long parts_total = 0, outs_total = 0;
-  for (int p = 0; p < nranks; ++p) {
-    parts_total += all[4 * p + 1];
-    outs_total += all[4 * p + 3];
-  }
-  if (parts_total != outs_total) return B2S_ERR_INVALID_ARG;  // extents must tile what was sorted
-  const unsigned char* src = static_cast<const unsigned char*>(part);
-  unsigned char* dst       = static_cast<unsigned char*>(out);
-  auto overlap = [](long long a0, long long a1, long long b0, long long b1, long long* lo, long long* hi) {
-    *lo = a0 > b0 ? a0 : b0;
-    *hi = a1 < b1 ? a1 : b1;
-    return *hi > *lo;
-  };
-  const long long ps = mine[0], pe = mine[0] + mine[1], os = mine[2], oe = mine[2] + mine[3];
-  if (barrier) barrier(barrier_ctx);
-  if (nranks > 1) CK_NCCL(ncclGroupStart());
-  for (int i = 1; i < nranks; ++i) {
-    const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
-    long long lo, hi;
-    if (overlap(ps, pe, all[4 * to + 2], all[4 * to + 2] + all[4 * to + 3], &lo, &hi))
-      CK_NCCL(ncclSend(src + (size_t)(lo - ps) * elem_bytes, (size_t)(hi - lo) * elem_bytes, ncclUint8, to, comm, stream));
-    if (overlap(all[4 * from], all[4 * from] + all[4 * from + 1], os, oe, &lo, &hi))
-      CK_NCCL(ncclRecv(dst + (size_t)(lo - os) * elem_bytes, (size_t)(hi - lo) * elem_bytes, ncclUint8, from, comm, stream));
-  }
-  if (nranks > 1) CK_NCCL(ncclGroupEnd());
-  if (barrier) barrier(barrier_ctx);
-  long long lo, hi;
-  if (overlap(ps, pe, os, oe, &lo, &hi))
-    CK_CUDA(cudaMemcpyAsync(dst + (size_t)(lo - os) * elem_bytes, src + (size_t)(lo - ps) * elem_bytes,
-                            (size_t)(hi - lo) * elem_bytes, cudaMemcpyDeviceToDevice, stream));
-  CK_CUDA(cudaStreamSynchronize(stream));
-  return B2S_OK;
-}
-
+// ---- NCCL communicator plumbing --------------------------------------------------------------
 int b2s_nccl_unique_id(void* out128)
 {
   static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
   if (out128 == nullptr) return B2S_ERR_INVALID_ARG;
-  CK_NCCL(ncclGetUniqueId(static_cast<ncclUniqueId*>(out128)));
-  return B2S_OK;
+  return ncclGetUniqueId(static_cast<ncclUniqueId*>(out128)) == ncclSuccess ? B2S_OK : B2S_ERR_NCCL;
 }
 
 int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank)
@@ -402,7 +664,7 @@ int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank)
   ncclUniqueId id;
   memcpy(&id, id128, sizeof(id));
   ncclComm_t c;
-  CK_NCCL(ncclCommInitRank(&c, nranks, id, rank));
+  if (ncclCommInitRank(&c, nranks, id, rank) != ncclSuccess) return B2S_ERR_NCCL;
   *comm = c;
   return B2S_OK;
 }
@@ -410,63 +672,127 @@ int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank)
 int b2s_nccl_comm_destroy(void* comm)
 {
   if (comm == nullptr) return B2S_OK;
-  CK_NCCL(ncclCommDestroy(static_cast<ncclComm_t>(comm)));
-  return B2S_OK;
+  return ncclCommDestroy(static_cast<ncclComm_t>(comm)) == ncclSuccess ? B2S_OK : B2S_ERR_NCCL;
 }
 
-int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
-                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
-                     void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
-                     size_t* out_len, int64_t* out_global_offset, void* cuda_stream)
+// ---- rebalance -----------------------------------------------------------------------------
+int b2s_dist_rebalance_1d_ops(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
+                              void* out, size_t out_len, int64_t out_global_start, const b2s_comm_ops* ops, int rank,
+                              int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                              b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
+{
+  if (elem_bytes == 0 || nranks < 1 || nranks > MAX_BUCKETS || rank < 0 || rank >= nranks || alloc == nullptr)
+    return B2S_ERR_INVALID_ARG;
+  if ((part_len > 0 && part == nullptr) || (out_len > 0 && out == nullptr)) return B2S_ERR_INVALID_ARG;
+  if (nranks > 1 && ops == nullptr) return B2S_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  Scratch mem{alloc, release, alloc_ctx, {}};
+  Status st;
+  // every rank learns where every rank's sorted part and output extent lie in the global order,
+  // and whether it got this far in one piece
+  long long mine[8] = {(long long)part_global_start, (long long)part_len, (long long)out_global_start, (long long)out_len, 0, 0, 0, 0};
+  std::vector<long long> all((size_t)8 * nranks);
+  if (nranks == 1) {
+    std::copy(mine, mine + 8, all.begin());
+  } else {
+    long long* d_all = static_cast<long long*>(mem.get(sizeof(long long) * 8 * (nranks + 1)));
+    if (d_all == nullptr) {
+      st.set(B2S_ERR_WORKSPACE);
+      d_all = reinterpret_cast<long long*>(emergency_area());
+      if (d_all == nullptr) return B2S_ERR_CUDA;  // no device memory at all to take part with
+    }
+    mine[4] = st.code;
+    st.cuda(cudaMemcpyAsync(d_all + 8 * nranks, mine, sizeof(mine), cudaMemcpyHostToDevice, stream));
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->all_gather(ops->ctx, d_all + 8 * nranks, d_all, sizeof(mine), stream));
+    if (barrier) barrier(barrier_ctx);
+    st.cuda(cudaMemcpyAsync(all.data(), d_all, sizeof(long long) * 8 * nranks, cudaMemcpyDeviceToHost, stream));
+    st.cuda(cudaStreamSynchronize(stream));
+    if (!st.ok()) return st.code;  // nothing the others sent can be trusted either
+  }
+  long long parts_total = 0, outs_total = 0;
+  int worst = B2S_OK;
+  for (int p = 0; p < nranks; ++p) {
+    parts_total += all[8 * p + 1];
+    outs_total += all[8 * p + 3];
+    if (all[8 * p + 4] != B2S_OK) worst = (int)all[8 * p + 4];
+  }
+  if (worst != B2S_OK) return worst;                            // every rank sees the same flags
+  if (parts_total != outs_total) return B2S_ERR_INVALID_ARG;    // extents must tile what was sorted
+  const unsigned char* src = static_cast<const unsigned char*>(part);
+  unsigned char* dst       = static_cast<unsigned char*>(out);
+  auto overlap = [](long long a0, long long a1, long long b0, long long b1, long long* lo, long long* hi) {
+    *lo = a0 > b0 ? a0 : b0;
+    *hi = a1 < b1 ? a1 : b1;
+    return *hi > *lo;
+  };
+  const long long ps = mine[0], pe = mine[0] + mine[1], os = mine[2], oe = mine[2] + mine[3];
+  if (nranks > 1) {
+    std::vector<const void*> sp(nranks, nullptr);
+    std::vector<void*> rp(nranks, nullptr);
+    std::vector<size_t> sb(nranks, 0), rb(nranks, 0);
+    for (int p = 0; p < nranks; ++p) {
+      if (p == rank) continue;
+      long long lo, hi;
+      if (overlap(ps, pe, all[8 * p + 2], all[8 * p + 2] + all[8 * p + 3], &lo, &hi)) {
+        sp[p] = src + (size_t)(lo - ps) * elem_bytes;
+        sb[p] = (size_t)(hi - lo) * elem_bytes;
+      }
+      if (overlap(all[8 * p], all[8 * p] + all[8 * p + 1], os, oe, &lo, &hi)) {
+        rp[p] = dst + (size_t)(lo - os) * elem_bytes;
+        rb[p] = (size_t)(hi - lo) * elem_bytes;
+      }
+    }
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->exchange(ops->ctx, sp.data(), sb.data(), rp.data(), rb.data(), stream));
+    if (barrier) barrier(barrier_ctx);
+  }
+  long long lo, hi;
+  if (overlap(ps, pe, os, oe, &lo, &hi))
+    st.cuda(cudaMemcpyAsync(dst + (size_t)(lo - os) * elem_bytes, src + (size_t)(lo - ps) * elem_bytes,
+                            (size_t)(hi - lo) * elem_bytes, cudaMemcpyDeviceToDevice, stream));
+  st.cuda(cudaStreamSynchronize(stream));
+  return st.code;
+}
+
+// ---- the distributed sort ---------------------------------------------------------------------
+int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
+                         const b2s_comm_ops* ops, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                         void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
+                         size_t* out_len, int64_t* out_global_offset, void* cuda_stream)
 {
   int xf       = 0;
   const int kb = kb_of(dtype, &xf);
   if (kb == 0) return B2S_ERR_UNSUPPORTED;
   if (alloc == nullptr || out_ptr == nullptr || out_len == nullptr || nranks < 1 || rank < 0 || rank >= nranks)
     return B2S_ERR_INVALID_ARG;
-  if (nranks > MERGE_MAX_RUNS) return B2S_ERR_UNSUPPORTED;
-  if (nranks > 1 && nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
+  if (nranks > MAX_BUCKETS) return B2S_ERR_UNSUPPORTED;
+  if (nranks > 1 && (ops == nullptr || ops->all_gather == nullptr || ops->barrier == nullptr || ops->exchange == nullptr))
+    return B2S_ERR_INVALID_ARG;
   if (n_local > 0 && keys_in == nullptr) return B2S_ERR_INVALID_ARG;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  ncclComm_t comm     = static_cast<ncclComm_t>(nccl_comm);
   Scratch mem{alloc, release, alloc_ctx, {}};
   const long long n = (long long)n_local;
+  const size_t out_elem = argsort ? 8 : (size_t)kb;
   PhaseTrace trace(rank);
-  int local_status = B2S_OK;
 
-  // ---- 1. local sort; indices are global positions (sort.cu:1851-1854) ----
-  // With more than one rank an argsort carries 32-bit local positions through the exchange where
-  // the local sort can produce them; the merge adds the source rank's offset.  Each rank tells
-  // the others which form it sends (payload width and offset travel with the cut positions).
-  const bool pos32 = argsort && nranks > 1 && local_sort_pos32_supported(n_local);
-  const size_t pb  = pos32 ? 4 : 8;  // bytes per payload element I send
-  // 16 spare bytes: the peer-memory exchange copies whole 16-byte vectors out of these buffers
-  void* keys       = mem.get((size_t)n * kb + 16);
-  unsigned char* idx = argsort ? static_cast<unsigned char*>(mem.get((size_t)n * pb + 16)) : nullptr;
-  if (keys == nullptr || (argsort && idx == nullptr)) return B2S_ERR_WORKSPACE;
-  void* sort_ws = nullptr;
-  if (n > 0) {
-    size_t ws_bytes = 0;
-    int rc = b2s_workspace_bytes(dtype, n_local, n_local, argsort, &ws_bytes);
-    if (rc != B2S_OK) return rc;
-    void* ws = mem.get(ws_bytes);
-    if (ws == nullptr) return B2S_ERR_WORKSPACE;
-    sort_ws = ws;
-    if (pos32)
-      rc = local_sort_pos32(dtype, keys_in, keys, reinterpret_cast<uint32_t*>(idx), n_local, ws, ws_bytes, stream);
-    else
-      rc = b2s_local_sort(dtype, keys_in, keys, reinterpret_cast<int64_t*>(idx), n_local, n_local, global_offset, 1, 1,
-                          ws, ws_bytes, stream);
-    if (rc != B2S_OK) return rc;
-    if (nranks == 1) {
-      rc = b2s_check_status(ws, stream);
+  // ---- one rank: the local sort, result in allocator memory ----
+  if (nranks == 1) {
+    void* result = mem.get(n_local * out_elem);
+    if (result == nullptr) return B2S_ERR_WORKSPACE;
+    if (n > 0) {
+      size_t ws_bytes = 0;
+      int rc = b2s_workspace_bytes(dtype, n_local, n_local, argsort, &ws_bytes);
+      if (rc != B2S_OK) return rc;
+      void* ws = mem.get(ws_bytes);
+      if (ws == nullptr) return B2S_ERR_WORKSPACE;
+      rc = b2s_local_sort(dtype, keys_in, argsort ? nullptr : result, argsort ? static_cast<int64_t*>(result) : nullptr, n_local,
+                          n_local, global_offset, 1, 1, ws, ws_bytes, stream);
+      if (rc != B2S_OK) return rc;
+      rc = dtype == B2S_COMPLEX128 ? (cudaStreamSynchronize(stream) == cudaSuccess ? B2S_OK : B2S_ERR_CUDA)
+                                   : b2s_check_status(ws, stream);
       if (rc != B2S_OK) return rc;
     }
-    // the workspace is released after the exchange below has synchronised the stream
-    if (nranks == 1) mem.drop(ws);
-  }
-  if (nranks == 1) {
-    void* result = argsort ? static_cast<void*>(idx) : keys;  // one rank: idx holds int64 global indices
     mem.disown(result);
     *out_ptr = result;
     *out_len = n_local;
@@ -474,277 +800,421 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
     return B2S_OK;
   }
 
-  trace.mark("enqueue_local_sort");
-  // ---- 2. samples: all-gather, order on the host, pick the splitters ----
-  // Each destination's value range is cut once more into PH consecutive sub-ranges ("phases"):
-  // while the runs of phase k are being merged, NCCL already moves the runs of phase k+1.
-  const int nph      = DIST_PHASES;  // the same on every rank by construction
-  const int nb       = nranks * nph;  // buckets: bucket q goes to rank q / nph in phase q % nph
-  const int s        = SAMPLES_PER_RANK;
-  // every rank's block of the first all-gather: its samples, then what the others need to read
-  // its sorted buffers directly (PeerRecord)
-  const size_t blk      = sizeof(Sample) * s + sizeof(PeerRecord);
-  unsigned char* d_blk  = static_cast<unsigned char*>(mem.get(blk * nranks));
-  Sample* d_split    = static_cast<Sample*>(mem.get(sizeof(Sample) * nb));
-  long long* d_cuts  = static_cast<long long*>(mem.get(sizeof(long long) * (nb + 4)));
-  long long* d_count = static_cast<long long*>(mem.get(sizeof(long long) * nranks * (nb + 4)));
-  int* d_done        = static_cast<int*>(mem.get(256));
-  if (!d_blk || !d_split || !d_cuts || !d_count || !d_done) return B2S_ERR_WORKSPACE;
-  PeerRecord my_rec;
-  {
-    void* bufs[PEER_BUFFERS] = {keys, idx};
-    export_buffers(bufs, argsort ? 2 : 1, &my_rec);
+  // From here on every rank goes through every collective, whatever happens to it locally: its
+  // status travels with the gathered blocks and all ranks return a failure together.
+  Status st;
+  const int nb  = nranks;
+  int nbp       = 1;
+  while (nbp < nb) nbp <<= 1;                       // padded bucket count
+  const int S_all            = nranks * SAMPLES_PER_RANK;
+  const long long ntiles     = (n + PART_TILE - 1) / PART_TILE;
+  const long long capacity   = n + n / 8 + 65536;  // elements my receive buffers hold
+  const size_t pay_cap_bytes = argsort ? 8 : 0;     // per element, enough for either payload width
+
+  // ---- control block: one allocation ----
+  size_t off = 0;
+  auto take  = [&](size_t bytes) { const size_t at = off; off += align_up(bytes, 256); return at; };
+  const size_t o_mineA = take(sizeof(BlockA)), o_allA = take(sizeof(BlockA) * nranks);
+  const size_t o_samples = take(sizeof(Sample) * S_all), o_khi = take(8 * (size_t)S_all), o_klo = take(8 * (size_t)S_all);
+  const size_t o_tmp = take(8 * (size_t)S_all), o_ord1 = take(8 * (size_t)S_all), o_ord2 = take(8 * (size_t)S_all);
+  const size_t o_cum = take(8 * (size_t)S_all), o_split = take(sizeof(Sample) * MAX_BUCKETS);
+  const size_t o_local = take(sizeof(LocalSplitter) * MAX_BUCKETS);
+  const size_t o_counts = take(4 * (size_t)(ntiles > 0 ? ntiles : 1) * nbp), o_toff = take(8 * (size_t)(ntiles > 0 ? ntiles : 1) * nbp);
+  const size_t o_totals = take(8 * MAX_BUCKETS), o_mineB = take(sizeof(BlockB)), o_allB = take(sizeof(BlockB) * nranks);
+  size_t sample_ws_bytes = 0;
+  b2s_workspace_bytes(B2S_UINT64, (size_t)S_all, (size_t)S_all, 1, &sample_ws_bytes);
+  const size_t o_sws = take(sample_ws_bytes);
+  unsigned char* ctl = static_cast<unsigned char*>(mem.get(off));
+  bool have_ctl      = ctl != nullptr;
+  if (!have_ctl) {
+    st.set(B2S_ERR_WORKSPACE);
+    ctl = emergency_area();
+    if (ctl == nullptr) return B2S_ERR_CUDA;  // not even the library's own device memory answers
   }
+  // receive buffers the other ranks write into
+  void* recv_keys = have_ctl ? mem.get((size_t)capacity * kb + 256) : nullptr;
+  void* recv_pay  = (have_ctl && argsort) ? mem.get((size_t)capacity * pay_cap_bytes + 256) : nullptr;
+  if (have_ctl && (recv_keys == nullptr || (argsort && recv_pay == nullptr))) st.set(B2S_ERR_WORKSPACE);
+
+  BlockA* d_mineA = reinterpret_cast<BlockA*>(ctl + (have_ctl ? o_mineA : 0));
+  BlockA* d_allA  = reinterpret_cast<BlockA*>(ctl + (have_ctl ? o_allA : sizeof(BlockA)));
+  BlockA h_mineA{};
+  h_mineA.n_local       = n;
+  h_mineA.global_offset = global_offset;
+  h_mineA.capacity      = capacity;
   {
+    void* bufs[PEER_BUFFERS] = {recv_keys, recv_pay};
+    export_buffers(bufs, argsort ? 2 : 1, &h_mineA.rec);
+    if (!st.ok()) h_mineA.rec.ok = 0;
+  }
+  h_mineA.status = st.code;
+  // header first, then the samples straight into the block on the device
+  st.cuda(cudaMemcpyAsync(d_mineA, &h_mineA, offsetof(BlockA, okey), cudaMemcpyHostToDevice, stream));
+  if (st.ok()) {
     prof::Scope ps(prof::K_DIST, stream);
-    by_width(kb, [&](auto w) {
-      sample_kernel<decltype(w)::value><<<(s + 127) / 128, 128, 0, stream>>>(
-        keys, n, s, rank, xf, reinterpret_cast<Sample*>(d_blk + (size_t)rank * blk));
+    by_width16(kb, [&](auto w) {
+      constexpr int KB = decltype(w)::value;
+      sample_kernel<KB><<<(SAMPLES_PER_RANK + 255) / 256, 256, 0, stream>>>(
+        static_cast<const typename DKey<KB>::Raw*>(keys_in), n, xf, d_mineA->okey);
       return cudaSuccess;
     });
+    st.cuda(cudaGetLastError());
   }
-  CK_CUDA(cudaGetLastError());
-  CK_CUDA(cudaMemcpyAsync(d_blk + (size_t)rank * blk + sizeof(Sample) * s, &my_rec, sizeof(PeerRecord),
-                          cudaMemcpyHostToDevice, stream));
   if (barrier) barrier(barrier_ctx);
-  CK_NCCL(ncclAllGather(d_blk + (size_t)rank * blk, d_blk, blk, ncclUint8, comm, stream));
+  st.set(ops->all_gather(ops->ctx, d_mineA, d_allA, sizeof(BlockA), stream));
   if (barrier) barrier(barrier_ctx);
-  std::vector<unsigned char> h_blk(blk * nranks);
-  std::vector<Sample> h_samples((size_t)s * nranks), h_split(nb);
-  CK_CUDA(cudaMemcpyAsync(h_blk.data(), d_blk, blk * nranks, cudaMemcpyDeviceToHost, stream));
-  CK_CUDA(cudaStreamSynchronize(stream));
-  std::vector<PeerRecord> recs(nranks);
-  for (int p = 0; p < nranks; ++p) {
-    std::memcpy(&h_samples[(size_t)p * s], &h_blk[(size_t)p * blk], sizeof(Sample) * s);
-    std::memcpy(&recs[p], &h_blk[(size_t)p * blk + sizeof(Sample) * s], sizeof(PeerRecord));
-  }
-  // Can I read everybody's buffers?  All ranks see the same records, so they agree on the first
-  // part; whether the mappings open is local and travels with the cut positions below.
-  std::vector<const unsigned char*> peer_keys(nranks, nullptr), peer_idx(nranks, nullptr);
-  PeerPins pins;  // declared after `mem` and before any kernel that reads a peer is launched
-  long long can_pull = 1;
-  for (int p = 0; p < nranks && can_pull; ++p) {
-    if (!recs[p].ok || recs[p].nbuf != (unsigned long long)(argsort ? 2 : 1)) can_pull = 0;
-    if (p != rank && recs[p].pid == my_rec.pid) can_pull = 0;
-  }
-  for (int p = 0; p < nranks && can_pull; ++p) {
-    if (p == rank) continue;
-    const unsigned char* kbase = static_cast<const unsigned char*>(pins.acquire(recs[p].handle[0]));
-    const unsigned char* ibase = argsort ? static_cast<const unsigned char*>(pins.acquire(recs[p].handle[1])) : nullptr;
-    if (kbase == nullptr || (argsort && ibase == nullptr)) {
-      can_pull = 0;
-      break;
-    }
-    peer_keys[p] = kbase + recs[p].off[0];
-    peer_idx[p]  = argsort ? ibase + recs[p].off[1] : nullptr;
-  }
-  trace.mark("local_sort+samples(sync)");
-  if (sort_ws != nullptr) {
-    // a wait inside the local sort that ran out shows up here; every rank still goes on to the
-    // collectives below so that nobody is left waiting, and the error is returned at the end
-    const int st = b2s_check_status(sort_ws, stream);
-    if (st != B2S_OK) local_status = st;
-  }
-  b2s_host_select_splitters(h_samples.data(), h_samples.size(), nb, h_split.data());
-  CK_CUDA(cudaMemcpyAsync(d_split, h_split.data(), sizeof(Sample) * (nb - 1), cudaMemcpyHostToDevice, stream));
+  // the headers come to the host while the device goes on with the splitters
+  std::vector<BlockA> h_allA_hdr(nranks);
+  std::vector<unsigned char> h_hdr((size_t)nranks * offsetof(BlockA, okey));
+  st.cuda(cudaMemcpy2DAsync(h_hdr.data(), offsetof(BlockA, okey), d_allA, sizeof(BlockA), offsetof(BlockA, okey), nranks,
+                            cudaMemcpyDeviceToHost, stream));
+  Event ev_hdr;
+  if (ev_hdr.ev == nullptr) st.set(B2S_ERR_CUDA); else st.cuda(cudaEventRecord(ev_hdr.ev, stream));
+  trace.mark("samples");
 
-  // ---- 3. where the splitters cut my data; every rank learns every rank's cut positions ----
+  // ---- splitters on the device: order the samples by (key, rank, position), weigh, pick ----
+  Sample* d_samples     = reinterpret_cast<Sample*>(ctl + o_samples);
+  LocalSplitter* d_local = reinterpret_cast<LocalSplitter*>(ctl + o_local);
+  unsigned int* d_counts = reinterpret_cast<unsigned int*>(ctl + o_counts);
+  unsigned long long* d_toff = reinterpret_cast<unsigned long long*>(ctl + o_toff);
+  long long* d_totals    = reinterpret_cast<long long*>(ctl + o_totals);
+  if (have_ctl && st.ok()) {
+    unsigned long long* khi = reinterpret_cast<unsigned long long*>(ctl + o_khi);
+    unsigned long long* klo = reinterpret_cast<unsigned long long*>(ctl + o_klo);
+    unsigned long long* tmp = reinterpret_cast<unsigned long long*>(ctl + o_tmp);
+    int64_t* ord1 = reinterpret_cast<int64_t*>(ctl + o_ord1);
+    int64_t* ord2 = reinterpret_cast<int64_t*>(ctl + o_ord2);
+    int64_t* order = ord1;
+    {
+      prof::Scope ps(prof::K_DIST, stream);
+      build_samples_kernel<<<(S_all + 255) / 256, 256, 0, stream>>>(d_allA, nranks, d_samples, khi, klo);
+    }
+    if (kb == 16) {
+      // two-word keys: stable order by the minor word, then by the major one
+      st.set(b2s_local_sort(B2S_UINT64, klo, nullptr, ord1, (size_t)S_all, (size_t)S_all, 0, 1, 1, ctl + o_sws, sample_ws_bytes, stream));
+      {
+        prof::Scope ps(prof::K_DIST, stream);
+        gather_u64_kernel<<<(S_all + 255) / 256, 256, 0, stream>>>(khi, ord1, S_all, tmp);
+      }
+      st.set(b2s_local_sort(B2S_UINT64, tmp, nullptr, ord2, (size_t)S_all, (size_t)S_all, 0, 1, 1, ctl + o_sws, sample_ws_bytes, stream));
+      {
+        prof::Scope ps(prof::K_DIST, stream);
+        compose_kernel<<<(S_all + 255) / 256, 256, 0, stream>>>(ord1, ord2, S_all, reinterpret_cast<int64_t*>(tmp));
+      }
+      order = reinterpret_cast<int64_t*>(tmp);
+    } else {
+      st.set(b2s_local_sort(B2S_UINT64, khi, nullptr, ord1, (size_t)S_all, (size_t)S_all, 0, 1, 1, ctl + o_sws, sample_ws_bytes, stream));
+    }
+    {
+      prof::Scope ps(prof::K_DIST, stream);
+      select_splitters_kernel<<<1, SELECT_THREADS, 0, stream>>>(d_samples, order, S_all, nb, rank,
+                                                                reinterpret_cast<long long*>(ctl + o_cum),
+                                                                reinterpret_cast<Sample*>(ctl + o_split), d_local, nbp - 1 > 0 ? nbp - 1 : 1);
+    }
+    // ---- count my elements per destination ----
+    if (n > 0) {
+      {
+        prof::Scope ps(prof::K_DIST, stream);
+        by_width16(kb, [&](auto w) {
+          constexpr int KB = decltype(w)::value;
+          part_count_kernel<KB><<<(unsigned int)ntiles, PART_THREADS, 0, stream>>>(
+            static_cast<const typename DKey<KB>::Raw*>(keys_in), n, xf, d_local, nbp, d_counts);
+          return cudaSuccess;
+        });
+      }
+      {
+        prof::Scope ps(prof::K_DIST, stream);
+        tile_scan_kernel<<<nbp, SCAN_THREADS, 0, stream>>>(d_counts, ntiles, nbp, d_toff, d_totals);
+      }
+    } else {
+      st.cuda(cudaMemsetAsync(d_totals, 0, 8 * MAX_BUCKETS, stream));
+    }
+    st.cuda(cudaGetLastError());
+  }
+
+  // ---- meanwhile on the host: who can write where ----
+  if (ev_hdr.ev != nullptr) st.cuda(cudaEventSynchronize(ev_hdr.ev)); else st.cuda(cudaStreamSynchronize(stream));
+  for (int p = 0; p < nranks; ++p) std::memcpy(&h_allA_hdr[p], &h_hdr[(size_t)p * offsetof(BlockA, okey)], offsetof(BlockA, okey));
+  PeerPins pins;  // declared after `mem`: the mappings are let go before the buffers
+  std::vector<unsigned char*> peer_keys(nranks, nullptr), peer_pay(nranks, nullptr);
+  long long mapped = st.ok() ? 1 : 0;
+  const unsigned long long my_pid = h_mineA.rec.pid;
+  for (int p = 0; p < nranks && mapped; ++p) {
+    const PeerRecord& r = h_allA_hdr[p].rec;
+    if (!r.ok || r.nbuf != (unsigned long long)(argsort ? 2 : 1)) { mapped = 0; break; }
+    if (p == rank) {
+      peer_keys[p] = static_cast<unsigned char*>(recv_keys);
+      peer_pay[p]  = static_cast<unsigned char*>(recv_pay);
+    } else if (r.pid == my_pid) {
+      if (!same_process_reachable((int)r.device)) { mapped = 0; break; }
+      peer_keys[p] = reinterpret_cast<unsigned char*>((uintptr_t)r.ptr[0]);
+      peer_pay[p]  = argsort ? reinterpret_cast<unsigned char*>((uintptr_t)r.ptr[1]) : nullptr;
+    } else {
+      unsigned char* kbase = static_cast<unsigned char*>(pins.acquire(r.handle[0]));
+      unsigned char* pbase = argsort ? static_cast<unsigned char*>(pins.acquire(r.handle[1])) : nullptr;
+      if (kbase == nullptr || (argsort && pbase == nullptr)) { mapped = 0; break; }
+      peer_keys[p] = kbase + r.off[0];
+      peer_pay[p]  = argsort ? pbase + r.off[1] : nullptr;
+    }
+  }
+  trace.mark("map");
+
+  // ---- second all-gather: counts per destination, mapping flag, status ----
+  BlockB* d_mineB = reinterpret_cast<BlockB*>(ctl + (have_ctl ? o_mineB : 0));
+  BlockB* d_allB  = reinterpret_cast<BlockB*>(ctl + (have_ctl ? o_allB : sizeof(BlockB)));
   {
-    prof::Scope ps(prof::K_DIST, stream);
-    by_width(kb, [&](auto w) {
-      cut_kernel<decltype(w)::value><<<(nb + 63) / 64, 64, 0, stream>>>(keys, n, d_split, nb, rank, xf, d_cuts,
-                                                                        (long long)pb, (long long)global_offset, can_pull);
-      return cudaSuccess;
-    });
+    BlockB hb{};
+    hb.status = st.code;
+    hb.mapped = mapped;
+    // the totals go from the device array straight into the block
+    st.cuda(cudaMemcpyAsync(d_mineB, &hb, offsetof(BlockB, total), cudaMemcpyHostToDevice, stream));
+    if (have_ctl) st.cuda(cudaMemcpyAsync(d_mineB->total, d_totals, 8 * MAX_BUCKETS, cudaMemcpyDeviceToDevice, stream));
   }
-  CK_CUDA(cudaGetLastError());
-  const size_t row = (size_t)nb + 4;  // nb + 1 cut positions, payload width, global offset, can-pull flag
-  std::vector<long long> h_allcuts((size_t)nranks * row);
   if (barrier) barrier(barrier_ctx);
-  CK_NCCL(ncclAllGather(d_cuts, d_count, sizeof(long long) * row, ncclUint8, comm, stream));
+  st.set(ops->all_gather(ops->ctx, d_mineB, d_allB, sizeof(BlockB), stream));
   if (barrier) barrier(barrier_ctx);
-  CK_CUDA(cudaMemcpyAsync(h_allcuts.data(), d_count, sizeof(long long) * nranks * row, cudaMemcpyDeviceToHost, stream));
-  CK_CUDA(cudaStreamSynchronize(stream));
-  trace.mark("cuts+counts(sync)");
-  for (int src = 0; src < nranks; ++src)
-    for (int q = 0; q < nb; ++q)
-      if (h_allcuts[src * row + q] > h_allcuts[src * row + q + 1]) return B2S_ERR_INVALID_ARG;  // protocol mismatch
-  bool use_pull = true;  // the same on every rank: everybody sees everybody's flag
-  for (int src = 0; src < nranks; ++src) use_pull = use_pull && h_allcuts[src * row + nb + 3] == 1;
-  std::vector<size_t> pay_bytes(nranks);
-  for (int src = 0; src < nranks; ++src) {
-    const long long w = h_allcuts[src * row + nb + 1];
-    if (w != 4 && w != 8) return B2S_ERR_INVALID_ARG;
-    pay_bytes[src] = (size_t)w;
-  }
-  const long long* my_cuts = &h_allcuts[(size_t)rank * row];
-
-  // ---- 4. exchange and merge, phase by phase ----
-  // My slice [cuts[q], cuts[q+1]) of bucket q goes to rank q / nph.  A slice starts wherever its
-  // splitter cut the sorted data, usually not on a 16-byte boundary, and NCCL's copies are much
-  // slower from unaligned addresses: each transfer starts at the slice's start rounded down to
-  // XFER_ALIGN elements and the receiver, who knows the sender's cut positions, skips the
-  // leading elements.  Runs land on aligned offsets of the receive buffer.
-  constexpr long long XFER_ALIGN = 32;
-  std::vector<MergeRuns> runs(nph);
-  std::vector<std::vector<long long>> recv_off(nph, std::vector<long long>(nranks)), lead(nph, std::vector<long long>(nranks));
-  std::vector<long long> ph_total(nph, 0);
-  long long total = 0, slots = 0;
-  for (int ph = 0; ph < nph; ++ph) {
-    runs[ph]       = MergeRuns{};
-    runs[ph].nruns = nranks;
-    const int q    = rank * nph + ph;
+  std::vector<BlockB> h_allB(nranks);
+  st.cuda(cudaMemcpyAsync(h_allB.data(), d_allB, sizeof(BlockB) * nranks, cudaMemcpyDeviceToHost, stream));
+  st.cuda(cudaStreamSynchronize(stream));
+  trace.mark("count(sync)");
+  if (!st.ok()) return st.code;  // my own copy failed: what I hold of the others cannot be trusted
+  // Every rank sees the same blocks from here on, so every decision below is the same everywhere.
+  {
+    int worst = B2S_OK;
     for (int p = 0; p < nranks; ++p) {
-      const long long start = h_allcuts[p * row + q], end = h_allcuts[p * row + q + 1];
-      runs[ph].len[p] = end - start;
-      lead[ph][p]     = p == rank ? 0 : start % XFER_ALIGN;
-      recv_off[ph][p] = slots;
-      slots += (lead[ph][p] + runs[ph].len[p] + XFER_ALIGN - 1) / XFER_ALIGN * XFER_ALIGN;
-      ph_total[ph] += runs[ph].len[p];
+      if (h_allA_hdr[p].status != B2S_OK) worst = (int)h_allA_hdr[p].status;
+      if (h_allB[p].status != B2S_OK) worst = (int)h_allB[p].status;
     }
-    total += ph_total[ph];
-  }
-  unsigned char* r_keys = static_cast<unsigned char*>(mem.get((size_t)slots * kb));
-  unsigned char* r_idx  = argsort ? static_cast<unsigned char*>(mem.get((size_t)slots * 8)) : nullptr;
-  void* result          = mem.get((size_t)total * (argsort ? 8 : kb));
-  if (r_keys == nullptr || (argsort && r_idx == nullptr) || result == nullptr) return B2S_ERR_WORKSPACE;
-  std::vector<void*> tcuts(nph, nullptr);
-  for (int ph = 0; ph < nph; ++ph) {
+    if (worst != B2S_OK) return worst;
     for (int p = 0; p < nranks; ++p) {
-      runs[ph].keys[p] = r_keys + (size_t)(recv_off[ph][p] + lead[ph][p]) * kb;
-      // a run's payload sits at the same element offset as its keys, whatever its width
-      runs[ph].idx[p]      = argsort ? r_idx + (size_t)recv_off[ph][p] * 8 + (size_t)lead[ph][p] * pay_bytes[p] : nullptr;
-      runs[ph].idx_bytes[p] = (int)pay_bytes[p];
-      runs[ph].idx_base[p]  = pay_bytes[p] == 4 ? h_allcuts[p * row + nb + 2] : 0;
-    }
-    if (ph_total[ph] > 0) {
-      size_t mws = 0;
-      b2s_kway_merge_workspace_bytes((size_t)ph_total[ph], nranks, &mws);
-      tcuts[ph] = mem.get(mws);
-      if (tcuts[ph] == nullptr) return B2S_ERR_WORKSPACE;
-    }
-  }
-  const unsigned char* k_bytes = static_cast<const unsigned char*>(keys);
-  trace.mark("alloc_recv");
-
-  // The exchange runs on a stream of its own so that it overlaps the merges on the caller's.
-  cudaStream_t xs = exchange_stream();
-  if (xs == nullptr) return B2S_ERR_CUDA;
-  Events events;
-  cudaEvent_t ev_ready = events.make();
-  std::vector<cudaEvent_t> ev_done(nph, nullptr);
-  for (auto& e : ev_done) e = events.make();
-  if (ev_ready == nullptr) return B2S_ERR_CUDA;
-  for (auto e : ev_done)
-    if (e == nullptr) return B2S_ERR_CUDA;
-  CK_CUDA(cudaEventRecord(ev_ready, stream));
-  CK_CUDA(cudaStreamWaitEvent(xs, ev_ready, 0));
-  for (int ph = 0; ph < nph && use_pull; ++ph) {
-    // One kernel copies this phase's slices out of the other ranks' sorted buffers.  Their
-    // contents are final: the all-gather of the cut positions above completed after every
-    // rank's local sort in stream order.
-    PullPlan plan{};
-    for (int i = 1; i < nranks; ++i) {
-      const int from = (rank + i) % nranks;
-      if (runs[ph].len[from] <= 0) continue;
-      const long long start = h_allcuts[from * row + (size_t)rank * nph + ph];  // their slice for me
-      const long long a0    = start - lead[ph][from];
-      const size_t cnt      = (size_t)(lead[ph][from] + runs[ph].len[from]);
-      plan.src[plan.nseg]   = reinterpret_cast<const uint4*>(peer_keys[from] + (size_t)a0 * kb);
-      plan.dst[plan.nseg]   = reinterpret_cast<uint4*>(r_keys + (size_t)recv_off[ph][from] * kb);
-      plan.nvec[plan.nseg]  = (cnt * kb + 15) / 16;
-      ++plan.nseg;
-      if (argsort) {
-        plan.src[plan.nseg]  = reinterpret_cast<const uint4*>(peer_idx[from] + (size_t)a0 * pay_bytes[from]);
-        plan.dst[plan.nseg]  = reinterpret_cast<uint4*>(r_idx + (size_t)recv_off[ph][from] * 8);
-        plan.nvec[plan.nseg] = (cnt * pay_bytes[from] + 15) / 16;
-        ++plan.nseg;
+      long long sum = 0;
+      for (int b = 0; b < nb; ++b) {
+        if (h_allB[p].total[b] < 0) return B2S_ERR_INVALID_ARG;  // protocol mismatch
+        sum += h_allB[p].total[b];
       }
+      if (sum != h_allA_hdr[p].n_local) return B2S_ERR_INVALID_ARG;
     }
-    if (plan.nseg > 0) {
-      for (int i = 0; i < plan.nseg; ++i)
-        if (((reinterpret_cast<uintptr_t>(plan.src[i]) | reinterpret_cast<uintptr_t>(plan.dst[i])) & 15u) != 0)
-          return B2S_ERR_INVALID_ARG;  // cannot happen with 256-byte aligned buffers and 32-element starts
-      int dev = 0, sms = 148;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      plan.ctas_per_seg = (2 * sms + plan.nseg - 1) / plan.nseg;
-      prof::begin(prof::K_XCHG, xs);
-      pull_kernel<<<(unsigned int)(plan.nseg * plan.ctas_per_seg), PULL_THREADS, 0, xs>>>(plan);
-      prof::end(prof::K_XCHG, xs);
-      CK_CUDA(cudaGetLastError());
-    }
-    CK_CUDA(cudaEventRecord(ev_done[ph], xs));
   }
-  if (use_pull) {
-    // nobody may release or reuse its sorted buffers before every rank has finished reading
-    // them: a collective behind the copy kernels, which the final synchronisation waits for
-    CK_CUDA(cudaMemsetAsync(d_done, 0, sizeof(int), xs));
-    if (barrier) barrier(barrier_ctx);
-    CK_NCCL(ncclAllReduce(d_done, d_done, 1, ncclInt32, ncclSum, comm, xs));
-    if (barrier) barrier(barrier_ctx);
-  }
-  for (int ph = 0; ph < nph && !use_pull; ++ph) {
-    if (barrier) barrier(barrier_ctx);
-    prof::begin(prof::K_XCHG, xs);
-    CK_NCCL(ncclGroupStart());
-    for (int i = 1; i < nranks; ++i) {
-      const int to = (rank + i) % nranks, from = (rank - i + nranks) % nranks;
-      const long long c0 = my_cuts[to * nph + ph], c1 = my_cuts[to * nph + ph + 1];
-      if (c1 > c0) {
-        const long long a0 = c0 - c0 % XFER_ALIGN;
-        const size_t cnt   = (size_t)(c1 - a0);
-        CK_NCCL(ncclSend(k_bytes + (size_t)a0 * kb, cnt * kb, ncclUint8, to, comm, xs));
-        if (argsort) CK_NCCL(ncclSend(idx + (size_t)a0 * pb, cnt * pb, ncclUint8, to, comm, xs));
-      }
-      if (runs[ph].len[from] > 0) {
-        const size_t cnt = (size_t)(lead[ph][from] + runs[ph].len[from]);
-        CK_NCCL(ncclRecv(r_keys + (size_t)recv_off[ph][from] * kb, cnt * kb, ncclUint8, from, comm, xs));
-        if (argsort)
-          CK_NCCL(ncclRecv(r_idx + (size_t)recv_off[ph][from] * 8, cnt * pay_bytes[from], ncclUint8, from, comm, xs));
-      }
+  std::vector<long long> recv_total(nranks, 0);
+  std::vector<std::vector<long long>> recv_off(nranks, std::vector<long long>(nranks, 0));  // [dst][src]
+  long long gmin = 0, gmax = 0, total_all = 0;
+  bool any = false, direct = true;
+  for (int d = 0; d < nranks; ++d) {
+    for (int s = 0; s < nranks; ++s) {
+      recv_off[d][s] = recv_total[d];
+      recv_total[d] += h_allB[s].total[d];
     }
-    CK_NCCL(ncclGroupEnd());
-    prof::end(prof::K_XCHG, xs);
-    if (barrier) barrier(barrier_ctx);
-    CK_CUDA(cudaEventRecord(ev_done[ph], xs));
-  }
-  trace.mark("enqueue_exchange");
-
-  // ---- 5. per phase: my own slice, then the stable k-way merge in rank order ----
-  long long out_off = 0;
-  for (int ph = 0; ph < nph; ++ph) {
-    const long long c0 = my_cuts[rank * nph + ph], c1 = my_cuts[rank * nph + ph + 1];
-    if (c1 > c0) {  // my own slice stays on this GPU
-      CK_CUDA(cudaMemcpyAsync(r_keys + (size_t)recv_off[ph][rank] * kb, k_bytes + (size_t)c0 * kb,
-                              (size_t)(c1 - c0) * kb, cudaMemcpyDeviceToDevice, stream));
-      if (argsort)
-        CK_CUDA(cudaMemcpyAsync(r_idx + (size_t)recv_off[ph][rank] * 8, idx + (size_t)c0 * pb, (size_t)(c1 - c0) * pb,
-                                cudaMemcpyDeviceToDevice, stream));
+    if (recv_total[d] > h_allA_hdr[d].capacity) direct = false;  // a receive buffer is too small for direct writes
+    if (!h_allB[d].mapped) direct = false;
+    if (h_allA_hdr[d].n_local > 0) {
+      const long long lo = h_allA_hdr[d].global_offset, hi = lo + h_allA_hdr[d].n_local;
+      gmin = any ? std::min(gmin, lo) : lo;
+      gmax = any ? std::max(gmax, hi) : hi;
+      any  = true;
     }
-    CK_CUDA(cudaStreamWaitEvent(stream, ev_done[ph], 0));
-    if (ph_total[ph] > 0) {
-      void* dst = static_cast<unsigned char*>(result) + (size_t)out_off * (argsort ? 8 : kb);
-      int rc    = merge_runs(kb, xf, runs[ph], ph_total[ph], argsort != 0, dst, static_cast<long long*>(tcuts[ph]), stream);
-      if (rc != B2S_OK) return rc;
-    }
-    out_off += ph_total[ph];
+    total_all += h_allA_hdr[d].n_local;
   }
-  trace.mark("enqueue_merge");
-  // temporaries are handed back only once the stream is done with them
-  CK_CUDA(cudaStreamSynchronize(stream));
-  CK_CUDA(cudaStreamSynchronize(xs));
-  trace.mark("exchange+merge(sync)");
-  mem.disown(result);
-  *out_ptr = result;
-  *out_len = (size_t)total;
+  const long long n_recv = recv_total[rank];
+  // payload of an argsort: global position minus the smallest one as 32 bits when that fits
+  const int payb = !argsort ? 0 : ((gmax - gmin) <= 0xFFFFFFFFll ? 4 : 8);
   if (out_global_offset) {
-    long long before = 0;  // elements that end up on lower ranks
-    for (int d = 0; d < rank; ++d)
-      for (int src = 0; src < nranks; ++src)
-        before += h_allcuts[src * row + (size_t)(d + 1) * nph] - h_allcuts[src * row + (size_t)d * nph];
+    long long before = 0;
+    for (int d = 0; d < rank; ++d) before += recv_total[d];
     *out_global_offset = before;
   }
-  return local_status;
+  if (total_all == 0) {
+    void* result = mem.get(256);
+    if (result == nullptr) return B2S_ERR_WORKSPACE;
+    mem.disown(result);
+    *out_ptr = result;
+    *out_len = 0;
+    return B2S_OK;
+  }
+
+  // ---- partition my tile into the destinations' receive buffers ----
+  void* send_keys = nullptr;
+  void* send_pay  = nullptr;
+  PartDst dst{};
+  if (direct) {
+    for (int d = 0; d < nranks; ++d) {
+      dst.keys[d] = peer_keys[d] + (size_t)recv_off[d][rank] * kb;
+      dst.pay[d]  = payb ? peer_pay[d] + (size_t)recv_off[d][rank] * payb : nullptr;
+    }
+  } else {
+    // the collective exchange: partition into a local buffer (bucket after bucket), send from it
+    send_keys = mem.get((size_t)n * kb + 256);
+    send_pay  = payb ? mem.get((size_t)n * payb + 256) : nullptr;
+    if (n_recv > capacity) {
+      recv_keys = mem.get((size_t)n_recv * kb + 256);
+      recv_pay  = payb ? mem.get((size_t)n_recv * payb + 256) : nullptr;
+    }
+    if (send_keys == nullptr || (payb && send_pay == nullptr) || recv_keys == nullptr || (payb && recv_pay == nullptr))
+      st.set(B2S_ERR_WORKSPACE);
+    long long at = 0;
+    for (int d = 0; d < nranks; ++d) {
+      dst.keys[d] = static_cast<unsigned char*>(send_keys) + (size_t)at * kb;
+      dst.pay[d]  = payb ? static_cast<unsigned char*>(send_pay) + (size_t)at * payb : nullptr;
+      at += h_allB[rank].total[d];
+    }
+    // one more agreement: a rank that could not allocate must not leave the others in the exchange
+    long long* d_flag = reinterpret_cast<long long*>(d_mineB);
+    const long long flag = st.code;
+    std::vector<long long> flags(nranks * (sizeof(BlockB) / 8));
+    st.cuda(cudaMemcpyAsync(d_flag, &flag, 8, cudaMemcpyHostToDevice, stream));
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->all_gather(ops->ctx, d_mineB, d_allB, sizeof(BlockB), stream));
+    if (barrier) barrier(barrier_ctx);
+    st.cuda(cudaMemcpyAsync(flags.data(), d_allB, sizeof(BlockB) * nranks, cudaMemcpyDeviceToHost, stream));
+    st.cuda(cudaStreamSynchronize(stream));
+    if (!st.ok()) return st.code;
+    for (int p = 0; p < nranks; ++p)
+      if (flags[p * (sizeof(BlockB) / 8)] != B2S_OK) return (int)flags[p * (sizeof(BlockB) / 8)];
+  }
+  if (n > 0) {
+    prof::Scope ps(prof::K_XCHG, stream);
+    by_width16(kb, [&](auto w) {
+      constexpr int KB = decltype(w)::value;
+      using Raw        = typename DKey<KB>::Raw;
+      auto launch = [&](auto kern, size_t bytes) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+        kern<<<(unsigned int)ntiles, PART_THREADS, bytes, stream>>>(static_cast<const Raw*>(keys_in), n, xf, d_local, nbp, d_toff,
+                                                                      dst, (long long)global_offset, gmin);
+        return cudaGetLastError();
+      };
+      if (payb == 0) return launch(part_scatter_kernel<KB, 0>, PartSmem<KB, 0>::BYTES);
+      if (payb == 4) return launch(part_scatter_kernel<KB, 4>, PartSmem<KB, 4>::BYTES);
+      return launch(part_scatter_kernel<KB, 8>, PartSmem<KB, 8>::BYTES);
+    });
+    st.cuda(cudaGetLastError());
+  }
+  if (direct) {
+    // nobody reads its receive buffer before everybody has finished writing into it, and nobody
+    // lets go of it before then either
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->barrier(ops->ctx, stream));
+    if (barrier) barrier(barrier_ctx);
+  } else {
+    std::vector<const void*> sp(nranks, nullptr);
+    std::vector<void*> rp(nranks, nullptr);
+    std::vector<size_t> sb(nranks, 0), rb(nranks, 0);
+    for (int pass = 0; pass < (payb ? 2 : 1); ++pass) {
+      const size_t eb = pass == 0 ? (size_t)kb : (size_t)payb;
+      unsigned char* sbase = static_cast<unsigned char*>(pass == 0 ? send_keys : send_pay);
+      unsigned char* rbase = static_cast<unsigned char*>(pass == 0 ? recv_keys : recv_pay);
+      long long at = 0;
+      for (int d = 0; d < nranks; ++d) {
+        sp[d] = sbase + (size_t)at * eb;
+        sb[d] = (size_t)h_allB[rank].total[d] * eb;
+        rp[d] = rbase + (size_t)recv_off[rank][d] * eb;
+        rb[d] = (size_t)h_allB[d].total[rank] * eb;
+        at += h_allB[rank].total[d];
+      }
+      if (sb[rank] > 0)  // my own piece stays on this GPU
+        st.cuda(cudaMemcpyAsync(rp[rank], sp[rank], sb[rank], cudaMemcpyDeviceToDevice, stream));
+      prof::begin(prof::K_XCHG, stream);
+      if (barrier) barrier(barrier_ctx);
+      st.set(ops->exchange(ops->ctx, sp.data(), sb.data(), rp.data(), rb.data(), stream));
+      if (barrier) barrier(barrier_ctx);
+      prof::end(prof::K_XCHG, stream);
+    }
+  }
+  trace.mark("partition");
+
+  // ---- sort what I received ----
+  void* result = mem.get((size_t)(n_recv > 0 ? n_recv : 1) * out_elem);
+  if (result == nullptr) st.set(B2S_ERR_WORKSPACE);
+  void* sort_ws = nullptr;
+  if (n_recv > 0 && st.ok()) {
+    size_t ws_bytes = 0;
+    st.set(b2s_workspace_bytes(dtype, (size_t)n_recv, (size_t)n_recv, argsort, &ws_bytes));
+    sort_ws = st.ok() ? mem.get(ws_bytes) : nullptr;
+    if (st.ok() && sort_ws == nullptr) st.set(B2S_ERR_WORKSPACE);
+    if (st.ok()) {
+      if (!argsort) {
+        st.set(b2s_local_sort(dtype, recv_keys, result, nullptr, (size_t)n_recv, (size_t)n_recv, 0, 1, 1, sort_ws, ws_bytes, stream));
+      } else if (payb == 4 && kb != 16 && local_sort_pos32_supported((size_t)n_recv) && (size_t)n_recv < single_limit()) {
+        // the radix passes carry the 32-bit payload themselves; the last one widens it
+        st.set(local_sort_payload32(dtype, recv_keys, static_cast<const uint32_t*>(recv_pay), static_cast<int64_t*>(result),
+                                    (size_t)n_recv, gmin, sort_ws, ws_bytes, stream));
+      } else {
+        // positions inside the receive buffer first, the payload through them afterwards
+        int64_t* position = static_cast<int64_t*>(mem.get((size_t)n_recv * 8));
+        if (position == nullptr) st.set(B2S_ERR_WORKSPACE);
+        if (st.ok())
+          st.set(b2s_local_sort(dtype, recv_keys, nullptr, position, (size_t)n_recv, (size_t)n_recv, 0, 1, 1, sort_ws, ws_bytes, stream));
+        if (st.ok()) {
+          prof::Scope ps(prof::K_DIST, stream);
+          unsigned int grid = (unsigned int)std::min<long long>((n_recv + 1023) / 1024, 148 * 16);
+          if (payb == 4)
+            gather_payload_kernel<uint32_t><<<grid, 256, 0, stream>>>(position, static_cast<const uint32_t*>(recv_pay), n_recv, gmin,
+                                                                       static_cast<int64_t*>(result));
+          else
+            gather_payload_kernel<int64_t><<<grid, 256, 0, stream>>>(position, static_cast<const int64_t*>(recv_pay), n_recv, 0,
+                                                                      static_cast<int64_t*>(result));
+          st.cuda(cudaGetLastError());
+        }
+      }
+    }
+  }
+  // temporaries are handed back only once the stream is done with them; a wait inside the local
+  // sort that ran out shows up here
+  if (sort_ws != nullptr && st.ok() && dtype != B2S_COMPLEX128) st.set(b2s_check_status(sort_ws, stream));
+  else st.cuda(cudaStreamSynchronize(stream));
+  trace.mark("sort(sync)");
+  if (!st.ok()) return st.code;
+  mem.disown(result);
+  *out_ptr = result;
+  *out_len = (size_t)n_recv;
+  return B2S_OK;
+}
+
+// The same two calls over an NCCL communicator.
+int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
+                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                     void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
+                     size_t* out_len, int64_t* out_global_offset, void* cuda_stream)
+{
+  if (nranks <= 1)
+    return b2s_dist_sort_1d_ops(dtype, keys_in, n_local, global_offset, argsort, nullptr, rank, nranks, alloc, release, alloc_ctx,
+                                barrier, barrier_ctx, out_ptr, out_len, out_global_offset, cuda_stream);
+  if (nccl_comm == nullptr || alloc == nullptr) return B2S_ERR_INVALID_ARG;
+  // the barrier's device word: from the caller's pool or, failing that, the library's own area
+  void* word     = alloc(alloc_ctx, 256);
+  const bool own = word != nullptr;
+  if (!own) {
+    unsigned char* ea = emergency_area();
+    if (ea == nullptr) return B2S_ERR_CUDA;
+    word = ea + EMERGENCY_BYTES - 256;
+  }
+  b2s_comm_ops ops{};
+  int rc = b2s_nccl_comm_ops(&ops, nccl_comm, rank, nranks, word);
+  if (rc == B2S_OK) {
+    cudaMemsetAsync(word, 0, sizeof(int), static_cast<cudaStream_t>(cuda_stream));
+    rc = b2s_dist_sort_1d_ops(dtype, keys_in, n_local, global_offset, argsort, &ops, rank, nranks, alloc, release, alloc_ctx,
+                              barrier, barrier_ctx, out_ptr, out_len, out_global_offset, cuda_stream);
+    b2s_nccl_comm_ops_release(&ops);
+  }
+  if (own && release) release(alloc_ctx, word);  // the call above synchronised the stream
+  return rc;
+}
+
+int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
+                          void* out, size_t out_len, int64_t out_global_start, void* nccl_comm, int rank,
+                          int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                          b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
+{
+  if (nranks <= 1)
+    return b2s_dist_rebalance_1d_ops(elem_bytes, part, part_len, part_global_start, out, out_len, out_global_start, nullptr, rank,
+                                     nranks, alloc, release, alloc_ctx, barrier, barrier_ctx, cuda_stream);
+  if (nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
+  int word = 0;  // the exchange of the rebalance needs no barrier word
+  b2s_comm_ops ops{};
+  int rc = b2s_nccl_comm_ops(&ops, nccl_comm, rank, nranks, &word);
+  if (rc != B2S_OK) return rc;
+  rc = b2s_dist_rebalance_1d_ops(elem_bytes, part, part_len, part_global_start, out, out_len, out_global_start, &ops, rank, nranks,
+                                 alloc, release, alloc_ctx, barrier, barrier_ctx, cuda_stream);
+  b2s_nccl_comm_ops_release(&ops);
+  return rc;
 }
 }

@@ -111,7 +111,8 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
 
 template <int KB, int XF>
 inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsigned int n,
-                               int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32)
+                               int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32,
+                               const uint32_t* idx_in)
 {
   using K            = typename KeyOf<KB>::type;
   const bool pairs   = idx_out != nullptr;
@@ -135,6 +136,7 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.keys_out    = out;
   ra.idx_out     = idx32 ? nullptr : idx_out;
   ra.idx_out32   = idx32 ? reinterpret_cast<uint32_t*>(idx_out) : nullptr;
+  ra.idx_in      = idx_in;
   ra.tmp_keys[0] = ws + lay.off_keys[0];
   ra.tmp_keys[1] = ws + lay.off_keys[1];
   ra.tmp_idx[0]  = reinterpret_cast<uint32_t*>(ws + lay.off_idx[0]);
@@ -245,9 +247,12 @@ cudaError_t launch_radix_seg(int xf, const void* in, void* out, int64_t* idx_out
 
 // 1-D stable sort of n < 2^30 keys. `ws` must hold radix_1d_layout<KB>(n, idx_out != null).total bytes.
 // idx32 != 0: idx_out points to n uint32 values and receives positions 0..n-1 without the offset.
+// idx_in != null: the payload of element i is idx_in[i] instead of i (stable argsort of data that
+// already carries 32-bit payloads); the output index is index_offset + payload.
 template <int KB>
 cudaError_t launch_radix_1d(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,
-                            int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32 = 0);
+                            int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32 = 0,
+                            const uint32_t* idx_in = nullptr);
 
 // Segments of seg_len <= SEG_CAP elements, sorted on chip. `ctrl` must be a zeroed control block.
 template <int KB>
@@ -292,14 +297,15 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
 #define B2S_INSTANTIATE_KEY_WIDTH(KB, HAS_FLOAT, HAS_CFLOAT)                                                          \
   template <>                                                                                             \
   cudaError_t launch_radix_1d<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,    \
-                                  int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32) \
+                                  int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32, \
+                                  const uint32_t* idx_in)                                                 \
   {                                                                                                       \
-    if (xf == XF_UNSIGNED) return radix_1d_xf<KB, XF_UNSIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
-    if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
+    if (xf == XF_UNSIGNED) return radix_1d_xf<KB, XF_UNSIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
+    if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
     if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
-      return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
+      return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
     if (HAS_CFLOAT && xf == XF_CFLOAT)                                                                    \
-      return radix_1d_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32); \
+      return radix_1d_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
     return cudaErrorInvalidValue;                                                                         \
   }                                                                                                       \
   template <>                                                                                             \

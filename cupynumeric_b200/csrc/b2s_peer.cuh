@@ -1,12 +1,13 @@
-// Peer-memory exchange of the distributed sort: every rank copies the slices it is owed straight
-// out of the other ranks' sorted buffers with its own kernel (plain loads over NVLink), instead of
-// pairing ncclSend/ncclRecv calls (the reference's exchange, src/cupynumeric/sort/sort.cu:1508-1745,
-// goes through NCCL as well).
+// Peer-memory side of the distributed sort: every rank writes the elements it owes another rank
+// straight into that rank's receive buffer with plain stores over NVLink, inside the kernel that
+// partitions its tile (the reference packs, then pairs ncclSend/ncclRecv calls,
+// src/cupynumeric/sort/sort.cu:1508-1745).
 //
-// The sorted buffers come from the caller's allocator, so they are made visible to the other
-// processes with CUDA IPC handles of the allocations they sit in.  Whatever cannot be exported
-// (memory that does not come from cudaMalloc, ranks living in one process) makes every rank fall
-// back to the NCCL exchange: each rank's "I can" flag travels with data all ranks see.
+// The receive buffers come from the caller's allocator.  Ranks that are processes of their own see
+// each other's buffers through CUDA IPC handles of the allocations they sit in; ranks that share
+// a process use the addresses directly.  Whatever cannot be reached (memory that does not come
+// from cudaMalloc, devices without peer access) makes every rank fall back to the collective
+// exchange of the b2s_comm_ops table: each rank's "I can" flag travels with data all ranks see.
 #pragma once
 #include <cuda_runtime.h>
 #include <unistd.h>
@@ -23,14 +24,16 @@ namespace b2s {
 
 constexpr int PEER_BUFFERS = 2;  // sorted keys, payload
 
-// What a rank publishes about its sorted buffers (fixed size, travels with the samples).
+// What a rank publishes about its receive buffers (fixed size, travels with the samples).
 struct PeerRecord {
   unsigned long long ok;                  // 1: the handles below can be opened
-  unsigned long long pid;                 // ranks of one process cannot open each other's handles
+  unsigned long long pid;                 // ranks of one process use `ptr` instead of the handles
   unsigned long long nbuf;                // buffers in use (1: keys only)
+  unsigned long long device;              // CUDA device ordinal inside the owner's process
+  unsigned long long ptr[PEER_BUFFERS];   // the buffer's address in the owner's process
   unsigned long long off[PEER_BUFFERS];   // byte offset of the buffer inside its allocation
   cudaIpcMemHandle_t handle[PEER_BUFFERS];
-  unsigned char pad_[256 - 8 * (3 + PEER_BUFFERS) - PEER_BUFFERS * sizeof(cudaIpcMemHandle_t)];
+  unsigned char pad_[256 - 8 * (4 + 2 * PEER_BUFFERS) - PEER_BUFFERS * sizeof(cudaIpcMemHandle_t)];
 };
 static_assert(sizeof(PeerRecord) == 256, "PeerRecord is a fixed 256-byte block");
 
@@ -64,18 +67,37 @@ inline void export_buffers(void* const* bufs, int nbuf, PeerRecord* rec)
   std::memset(rec, 0, sizeof(*rec));
   rec->pid  = (unsigned long long)getpid();
   rec->nbuf = (unsigned long long)nbuf;
+  int dev   = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  rec->device = (unsigned long long)dev;
   if (!peer_exchange_enabled()) return;
   for (int i = 0; i < nbuf; ++i) {
     unsigned long long base = 0;
     const uintptr_t p       = reinterpret_cast<uintptr_t>(bufs[i]);
-    if (bufs[i] == nullptr || (p & 255u) != 0 || !allocation_base(bufs[i], &base)) return;
+    if (bufs[i] == nullptr || (p & 255u) != 0) return;
+    rec->ptr[i] = (unsigned long long)p;
+    if (!allocation_base(bufs[i], &base)) return;
     if (cudaIpcGetMemHandle(&rec->handle[i], reinterpret_cast<void*>((uintptr_t)base)) != cudaSuccess) {
-      cudaGetLastError();  // not an error of the sort: the NCCL exchange takes over
+      cudaGetLastError();  // not an error of the sort: the collective exchange takes over
       return;
     }
     rec->off[i] = (unsigned long long)p - base;
   }
   rec->ok = 1;
+}
+
+// A buffer of a rank that lives in this process, on device `their_dev`: usable as it is on the
+// same device, after enabling peer access on another one.
+inline bool same_process_reachable(int their_dev)
+{
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (dev == their_dev) return true;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, dev, their_dev) != cudaSuccess || !can) return false;
+  const cudaError_t e = cudaDeviceEnablePeerAccess(their_dev, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+  return e == cudaSuccess || e == cudaErrorPeerAccessAlreadyEnabled;
 }
 
 // Mappings of other processes' allocations, opened once and kept: opening costs far more than a
@@ -148,8 +170,8 @@ class PeerMappings {
   unsigned long long clock_ = 0;
 };
 
-// The mappings one sort holds, unpinned when the sort returns: by then its copy kernels have
-// finished, because the sort synchronises its streams before it returns.
+// The mappings one sort holds, unpinned when the sort returns: by then every kernel that wrote
+// through them has finished, because the sort synchronises its stream before it returns.
 struct PeerPins {
   std::vector<std::string> keys;
   void* acquire(const cudaIpcMemHandle_t& h)
@@ -164,53 +186,5 @@ struct PeerPins {
     for (const auto& k : keys) PeerMappings::instance().release(k);
   }
 };
-
-// ---- the copy kernel ----
-constexpr int PULL_MAX_SEGS = 64;   // (MERGE_MAX_RUNS - 1) sources x PEER_BUFFERS
-constexpr int PULL_THREADS  = 512;
-constexpr int PULL_UNROLL   = 4;
-constexpr unsigned long long PULL_CHUNK = (unsigned long long)PULL_THREADS * PULL_UNROLL * 4;  // 16-byte vectors
-
-struct PullPlan {
-  const uint4* src[PULL_MAX_SEGS];  // another GPU's memory, 16-byte aligned
-  uint4* dst[PULL_MAX_SEGS];        // this GPU's memory, 16-byte aligned
-  unsigned long long nvec[PULL_MAX_SEGS];
-  int nseg;
-  int ctas_per_seg;
-};
-
-__device__ __forceinline__ uint4 load_peer(const uint4* p)
-{
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
-// CTA b works on segment b % nseg, so that at any time every source GPU is being read by some
-// CTAs of every destination: no source's links carry the whole exchange alone.
-static __global__ void __launch_bounds__(PULL_THREADS) pull_kernel(const __grid_constant__ PullPlan plan)
-{
-  const int seg                  = (int)(blockIdx.x % (unsigned int)plan.nseg);
-  const unsigned long long first = blockIdx.x / (unsigned int)plan.nseg;
-  const uint4* s                 = plan.src[seg];
-  uint4* d                       = plan.dst[seg];
-  const unsigned long long nv    = plan.nvec[seg];
-  for (unsigned long long c0 = first * PULL_CHUNK; c0 < nv; c0 += (unsigned long long)plan.ctas_per_seg * PULL_CHUNK) {
-    const unsigned long long c1 = c0 + PULL_CHUNK < nv ? c0 + PULL_CHUNK : nv;
-    for (unsigned long long v = c0 + threadIdx.x; v < c1; v += (unsigned long long)PULL_THREADS * PULL_UNROLL) {
-      uint4 r[PULL_UNROLL];
-#pragma unroll
-      for (int u = 0; u < PULL_UNROLL; ++u) {
-        const unsigned long long vv = v + (unsigned long long)u * PULL_THREADS;
-        if (vv < c1) r[u] = load_peer(s + vv);
-      }
-#pragma unroll
-      for (int u = 0; u < PULL_UNROLL; ++u) {
-        const unsigned long long vv = v + (unsigned long long)u * PULL_THREADS;
-        if (vv < c1) d[vv] = r[u];
-      }
-    }
-  }
-}
 
 }  // namespace b2s

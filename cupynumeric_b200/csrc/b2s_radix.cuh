@@ -90,6 +90,7 @@ struct RouteArgs {
   void* keys_out;     // may be null (argsort)
   int64_t* idx_out;   // may be null (sort)
   uint32_t* idx_out32; // instead of idx_out: positions without offset, 32 bits wide
+  const uint32_t* idx_in; // null: payloads are the element positions; else the caller's 32-bit payload
   void* tmp_keys[2];
   uint32_t* tmp_idx[2];
   unsigned int n;
@@ -125,7 +126,7 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
   int m = 0;
   for (int p = 0; p < a.npass; ++p) m += active[p];
   const void* cur_keys   = a.keys_in;
-  const uint32_t* cur_idx = nullptr;
+  const uint32_t* cur_idx = a.idx_in;
   FixDesc fix            = {};
   int j                  = 0;
   for (int p = 0; p < a.npass; ++p) {
@@ -165,6 +166,7 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
     }
     fix.synth_idx   = a.idx_out;
     fix.synth_idx32 = a.idx_out32;
+    fix.widen_src   = a.idx_in;
   }
   ctrl->fix = fix;
 }
@@ -241,7 +243,11 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
     }
   }
   if (f.synth_idx != nullptr) {
-    for (size_t i = gthread; i < n; i += gstride) f.synth_idx[i] = index_offset + (int64_t)i;
+    if (f.widen_src != nullptr) {
+      for (size_t i = gthread; i < n; i += gstride) f.synth_idx[i] = index_offset + (int64_t)f.widen_src[i];
+    } else {
+      for (size_t i = gthread; i < n; i += gstride) f.synth_idx[i] = index_offset + (int64_t)i;
+    }
   }
   if (f.synth_idx32 != nullptr) {
     for (size_t i = gthread; i < n; i += gstride) f.synth_idx32[i] = (uint32_t)i;

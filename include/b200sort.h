@@ -129,6 +129,38 @@ typedef void (*b2s_free_fn)(void* ctx, void* ptr);
  * May be NULL when each rank is a process of its own. */
 typedef void (*b2s_barrier_fn)(void* ctx);
 
+/* The collectives the distributed calls need, supplied by the host runtime.  All buffers are
+ * device memory of the calling rank; every rank of the group makes the same call with the same
+ * sizes, on its own stream.  Each function returns a b2s_status_t.
+ *   all_gather  every rank contributes `bytes` from `send` and receives the nranks contributions,
+ *               in rank order, in `recv`
+ *   barrier     completes on a rank's stream only after every rank has enqueued it behind its
+ *               earlier work on that stream
+ *   exchange    grouped point-to-point transfers: send send_bytes[p] bytes from send_ptr[p] to
+ *               rank p and receive recv_bytes[p] bytes from it into recv_ptr[p] (arrays of nranks
+ *               entries; the caller's own entry is ignored; zero sizes are skipped)
+ * In the reference these are ncclAllGather / grouped ncclSend+ncclRecv on the communicator Legate
+ * hands the task (src/cupynumeric/sort/sort.cu:1387-1413, 1687-1745). */
+typedef struct {
+  void* ctx;
+  int (*all_gather)(void* ctx, const void* send, void* recv, size_t bytes, void* cuda_stream);
+  int (*barrier)(void* ctx, void* cuda_stream);
+  int (*exchange)(void* ctx, const void* const* send_ptr, const size_t* send_bytes, void* const* recv_ptr,
+                  const size_t* recv_bytes, void* cuda_stream);
+} b2s_comm_ops;
+
+/* Fills `ops` with the NCCL form of the table for one rank of `nccl_comm`.  `barrier_word` is one
+ * zeroed int of device memory the barrier may use.  Release with b2s_nccl_comm_ops_release. */
+int b2s_nccl_comm_ops(b2s_comm_ops* ops, void* nccl_comm, int rank, int nranks, void* barrier_word);
+void b2s_nccl_comm_ops_release(b2s_comm_ops* ops);
+
+/* A group of `nranks` ranks that are threads of the calling process, synchronised on the host:
+ * fills ops_out[0..nranks-1], one table per rank, each to be used by one thread.  For hosts that
+ * drive several streams or GPUs from one process, and for exercising the multi-rank paths on a
+ * single GPU.  Every table is released with b2s_thread_comm_destroy. */
+int b2s_thread_comm_create(int nranks, b2s_comm_ops* ops_out);
+void b2s_thread_comm_destroy(b2s_comm_ops* ops);
+
 /* Sorts a 1-D array whose contiguous tiles live on the `nranks` GPUs of one communicator: rank
  * r holds `n_local` elements starting at global position `global_offset`.  Every rank of the
  * communicator must call, even with n_local == 0 (src/cupynumeric/sort/sort_template.inl:62-72).
@@ -137,12 +169,26 @@ typedef void (*b2s_barrier_fn)(void* ctx);
  * 0..nranks-1, concatenated, are the global stable sort.  The buffer belongs to the caller, as
  * with an unbound store's bind_data (sort.cu:1774-1783); *out_global_offset (may be NULL) is the
  * global position of its first element.  Synchronises the stream.
- * The slices move between the GPUs through a copy kernel that reads the other ranks' sorted
- * buffers in place when every rank's `alloc` returns cudaMalloc memory that CUDA IPC can export
- * and each rank is a process of its own; otherwise, or with B2S_DIST_P2P=0 in the environment,
- * through ncclSend/ncclRecv.  The result is the same either way.
+ *
+ * How it works: samples of the unsorted tiles are gathered, weighted splitters are chosen from
+ * them on the device, and each rank's partition kernel writes every element straight into the
+ * receive buffer of its destination GPU (plain stores through a peer mapping of that buffer); after
+ * one barrier each GPU sorts what it received.  The peer mappings need `alloc` to return cudaMalloc
+ * memory that CUDA IPC can export (ranks in processes of their own) or ranks that share a process;
+ * otherwise, when a receive buffer turns out too small, or with B2S_DIST_P2P=0 in the environment,
+ * the partition is written locally and moved with the table's `exchange`.  The result is the same
+ * either way.
+ *
+ * A failure that only one rank meets (its allocator returns NULL, a CUDA error) does not leave the
+ * others waiting: the rank keeps taking part in the collectives, its status travels with the
+ * gathered data and every rank returns the failure.
  * Replaces SortImplBody<GPU> for unbound 1-D outputs plus sample_sort_nccl_nd
  * (src/cupynumeric/sort/sort.cu:1797-1940 and 1270-1784). */
+int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
+                         const b2s_comm_ops* ops, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                         void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
+                         size_t* out_len, int64_t* out_global_offset, void* cuda_stream);
+/* The same call with the NCCL form of the table built from `nccl_comm`. */
 int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
                      void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
                      void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void** out_ptr,
@@ -154,6 +200,10 @@ int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t glo
  * parts cover.  Every rank calls.  This is what a bound, aligned output store needs after a
  * sample sort along a split axis; it replaces rebalance_data
  * (src/cupynumeric/sort/sort.cu:799-1261) for one segment at a time.  Synchronises the stream. */
+int b2s_dist_rebalance_1d_ops(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
+                              void* out, size_t out_len, int64_t out_global_start, const b2s_comm_ops* ops, int rank,
+                              int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                              b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream);
 int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, int64_t part_global_start,
                           void* out, size_t out_len, int64_t out_global_start, void* nccl_comm, int rank,
                           int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
@@ -161,9 +211,10 @@ int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, 
 
 /* Stable merge of `nruns` (<= 32) sorted runs, ties taken from the lower-numbered run first:
  * out receives the merged keys, or - when run_idx is not NULL - only the merged int64 payloads.
- * `ws`: b2s_kway_merge_workspace_bytes(total, nruns) bytes of device scratch.  This is the last
- * step of b2s_dist_sort_1d, exported on its own; it replaces merge_all_buffers
- * (src/cupynumeric/sort/sort.cu:608-790). */
+ * `ws`: b2s_kway_merge_workspace_bytes(total, nruns) bytes of device scratch.  One pass over the
+ * data whatever the run count; stands where the reference has merge_all_buffers
+ * (src/cupynumeric/sort/sort.cu:608-790).  b2s_local_sort uses it for 1-D tiles of 2^30 keys and
+ * more (sorted in chunks); the distributed sort needs no merge. */
 int b2s_kway_merge_workspace_bytes(size_t total, int nruns, size_t* bytes);
 int b2s_kway_merge(int dtype, int nruns, const void* const* run_keys, const int64_t* const* run_idx,
                    const size_t* run_len, void* out, void* ws, size_t ws_bytes, void* cuda_stream);
@@ -176,19 +227,26 @@ int b2s_nccl_comm_create(void** comm, int nranks, const void* id128, int rank);
 int b2s_nccl_comm_destroy(void* comm);
 
 /* Host-side pieces of the splitter logic, exported so that they can be exercised without a GPU.
- * A sample is the 24-byte record {uint64 ordered_key; int64 position; int32 rank; int32 valid}
- * (role of SegmentSample, src/cupynumeric/sort/sort.h:37-43). */
+ * A sample is the 48-byte record {uint64 okey_hi, okey_lo; int64 position; int64 weight; int32 rank;
+ * int32 pad}: a key in its order-preserving unsigned form (okey_lo is used by 16-byte keys only),
+ * its position in the owner's tile and the number of elements of that tile it stands for (0: slot
+ * not populated).  Role of SegmentSample, src/cupynumeric/sort/sort.h:37-43. */
 int b2s_samples_per_rank(void);
-/* Position of regular sample j of s in n >= s sorted elements (sort.cu:523-527). */
+/* Position and weight of regular sample j of s in a tile of n >= s elements (the reference takes
+ * its samples from the sorted tile, sort.cu:523-527; here they come from the unsorted one). */
 long long b2s_host_sample_position(long long j, long long s, long long n);
-/* Orders `count` samples by (ordered_key, rank, position), unpopulated ones last
+long long b2s_host_sample_weight(long long j, long long s, long long n);
+/* Orders `count` samples by (key, rank, position), unpopulated ones last
  * (SegmentSampleComparator, sort.h:60-81; thrust::stable_sort at sort.cu:1441-1445). */
 void b2s_host_sort_samples(void* samples, size_t count);
-/* Sorts the gathered samples and writes the nranks-1 splitters (sort.cu:1455-1470). */
-int b2s_host_select_splitters(void* samples, size_t count, int nranks, void* splitters_out);
-/* How many leading elements of rank my_rank's sorted data go left of the splitter, given the
- * counts of local keys below / not above the splitter's key (sort.cu:170-187). */
-long long b2s_host_cut_position(const void* splitter, int my_rank, long long lower, long long upper);
+/* Sorts the gathered samples and writes the nbuckets-1 splitters: splitter k is the first sample
+ * at which the cumulative weight reaches k/nbuckets of the total (sort.cu:1455-1470 picks by
+ * count; weights keep ragged tiles from skewing the cut). */
+int b2s_host_select_splitters(void* samples, size_t count, int nbuckets, void* splitters_out);
+/* Destination of the element (key, my_rank, pos): the number of splitters whose (key, rank,
+ * position) triple is smaller than the element's (sort.h:72-78, sort.cu:170-187). */
+int b2s_host_bucket_of(const void* splitters, int nsplit, int my_rank, unsigned long long okey_hi,
+                       unsigned long long okey_lo, long long pos);
 
 /* ---- SEARCHSORTED (the sorted output's natural consumer; a separate task in the reference) ---- */
 
@@ -226,9 +284,9 @@ typedef enum {
   B2S_K_FIXUP   = 3, /* leftover copies / synthesised indices */
   B2S_K_SEGSORT = 4, /* on-chip segmented sort */
   B2S_K_UNIT    = 5, /* segments of one element */
-  B2S_K_DIST    = 6, /* sampling, splitter search and cut kernels of the distributed sort */
+  B2S_K_DIST    = 6, /* sampling, splitter selection and counting kernels of the distributed sort */
   B2S_K_MERGE   = 7, /* k-way merge */
-  B2S_K_XCHG    = 8, /* NCCL key/index exchange of the distributed sort (timed, not counted as a launch) */
+  B2S_K_XCHG    = 8, /* the partition kernel that writes into the destinations' receive buffers (or the collective exchange) */
   B2S_K_COUNT   = 9
 } b2s_kernel_kind_t;
 

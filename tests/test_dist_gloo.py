@@ -1,8 +1,8 @@
-"""World-size-2 CPU test of the distributed sort's host logic over the gloo backend: regular
-sampling, splitter selection and the cut rule come from the C ABI's host entry points; the local
-sort and the final merge are played by the oracle, the exchange by gloo.  Checks that the
-rank-ordered concatenation is the global stable sort, that indices are global, and that the
-splitters balance heavy duplicates."""
+"""World-size-2 CPU test of the distributed sort's host logic over the gloo backend: where the
+samples are taken, the weighted splitter selection and the destination rule come from the C ABI's
+host entry points; the local sort of what a rank received is played by the oracle, the data
+movement by gloo.  Checks that the rank-ordered concatenation is the global stable sort, that
+indices are global, and that the splitters balance heavy duplicates."""
 import os
 import sys
 
@@ -43,8 +43,6 @@ def worker(rank: int, world: int, port: int, kind: str, n: int, argsort: bool, r
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from cupynumeric_b200 import _lib
-        from oracle import np_task_sort
-
         lib = _lib.lib()
         shard = make_shard(kind, rank, n)
         n_local = shard.size
@@ -52,53 +50,43 @@ def worker(rank: int, world: int, port: int, kind: str, n: int, argsort: bool, r
         dist.all_gather(lens, torch.tensor([n_local]))
         global_lo = int(sum(int(x) for x in lens[:rank]))
 
-        # local sort (oracle) with global indices
-        order = np_task_sort(shard, max(n_local, 1), True) if n_local else np.empty(0, np.int64)
-        keys = shard[order]
-        idx = order + global_lo
-        okeys = ordered_u64(keys)
+        okeys = ordered_u64(shard)
 
-        # regular samples, exactly as the device kernel takes them
+        # regular samples of the unsorted tile, exactly as the device kernel takes them
         s = lib.b2s_samples_per_rank()
         mine = np.zeros(s, dtype=_lib.SAMPLE_DTYPE)
         s_eff = min(s, n_local)
         for j in range(s):
             if j < s_eff:
                 p = lib.b2s_host_sample_position(j, s_eff, n_local)
-                mine[j] = (okeys[p], p, rank, 1)
+                mine[j] = (okeys[p], 0, p, lib.b2s_host_sample_weight(j, s_eff, n_local), rank, 0)
             else:
-                mine[j] = (np.uint64(2**64 - 1), 0, rank, 0)
+                mine[j] = (np.uint64(2**64 - 1), np.uint64(2**64 - 1), 0, 0, rank, 0)
+        assert int(mine["weight"].sum()) == n_local
         gathered = [torch.zeros(mine.nbytes, dtype=torch.uint8) for _ in range(world)]
         dist.all_gather(gathered, torch.from_numpy(mine.view(np.uint8)))
         samples = np.concatenate([g.numpy() for g in gathered]).view(_lib.SAMPLE_DTYPE).copy()
         splitters = np.zeros(world - 1, dtype=_lib.SAMPLE_DTYPE)
         assert lib.b2s_host_select_splitters(samples.ctypes.data, samples.size, world, splitters.ctypes.data) == 0
 
-        cuts = [0]
-        for k in range(world - 1):
-            sp = splitters[k:k + 1]
-            if not sp["valid"][0]:
-                cuts.append(n_local)
-                continue
-            lower = int(np.searchsorted(okeys, sp["okey"][0], side="left"))
-            upper = int(np.searchsorted(okeys, sp["okey"][0], side="right"))
-            cuts.append(int(lib.b2s_host_cut_position(sp.ctypes.data, rank, lower, upper)))
-        cuts.append(n_local)
-        assert all(a <= b for a, b in zip(cuts, cuts[1:])), cuts
-
-        # exchange
-        send_counts = torch.tensor([cuts[p + 1] - cuts[p] for p in range(world)])
+        # destination of every element of my tile; the pieces keep their input order
+        dest = np.array([lib.b2s_host_bucket_of(splitters.ctypes.data, world - 1, rank, int(okeys[i]), 0, i)
+                         for i in range(n_local)], dtype=np.int64)
+        assert ((dest >= 0) & (dest < world)).all()
+        idx = np.arange(n_local, dtype=np.int64) + global_lo
+        send_counts = torch.tensor([int((dest == p).sum()) for p in range(world)])
+        by_dest = np.argsort(dest, kind="stable")
         recv_counts = torch.zeros(world, dtype=torch.int64)
         dist.all_to_all_single(recv_counts, send_counts)
-        payload = idx if argsort else keys.view(np.int64)
         recv_k = torch.zeros(int(recv_counts.sum()), dtype=torch.int64)
         recv_p = torch.zeros(int(recv_counts.sum()), dtype=torch.int64)
-        dist.all_to_all_single(recv_k, torch.from_numpy(np.ascontiguousarray(keys.view(np.int64))),
+        dist.all_to_all_single(recv_k, torch.from_numpy(np.ascontiguousarray(shard[by_dest].view(np.int64))),
                                recv_counts.tolist(), send_counts.tolist())
-        dist.all_to_all_single(recv_p, torch.from_numpy(np.ascontiguousarray(payload)),
+        dist.all_to_all_single(recv_p, torch.from_numpy(np.ascontiguousarray(idx[by_dest])),
                                recv_counts.tolist(), send_counts.tolist())
         rk = recv_k.numpy().view(shard.dtype)
-        # runs arrive in rank order: a stable sort of their concatenation is the stable merge
+        # the pieces arrive in rank order, each in input order: a stable sort of what arrived is
+        # this rank's part of the global stable sort
         m = np.argsort(rk, kind="stable")
         part = recv_p.numpy()[m] if argsort else rk[m]
 
