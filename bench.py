@@ -47,9 +47,9 @@ L2_BYTES = 126 << 20
 # adds the k-way merge); nvlink_bytes: bytes per key that cross NVLink per direction, before the
 # (P-1)/P factor; sweep_bytes: algorithmic bytes per key of one launch of the dominant kernel.
 CONFIGS = {
-    "c1": dict(label="1-D int32 sort, N=2^{log2}, keys uniform over the full int32 range", dtype="i32", log2=24,
-               argsort=False, hbm_bytes=(36.0, 36.0), nvlink_bytes=0.0, sweep_bytes=8.0, kernel="onesweep_kernel",
-               multi="replicas"),
+    "c1": dict(label="1-D int32 sort, N=2^{log2} per GPU, keys uniform over the full int32 range", dtype="i32", log2=24,
+               argsort=False, hbm_bytes=(36.0, 36.0), nvlink_bytes=4.0, sweep_bytes=8.0, kernel="onesweep_kernel",
+               multi="distributed"),
     "c2": dict(label="1-D float32 stable argsort -> int64, N=2^{log2} per GPU, N(0,1) + 0.1% NaN + 1% duplicates",
                dtype="f32", log2=28, argsort=True, hbm_bytes=(88.0, 108.0), nvlink_bytes=12.0, sweep_bytes=21.0,
                kernel="onesweep_kernel", multi="distributed"),

@@ -34,6 +34,7 @@ int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in,
 }  // namespace b2s
 #include "b2s_dist_host.h"
 #include "b2s_merge.cuh"
+#include "b2s_partition.cuh"
 #include "b2s_prof.h"
 
 namespace b2s {
@@ -219,11 +220,18 @@ part_count_kernel(const typename DKey<KB>::Raw* __restrict__ keys, long long n, 
   if (tid < MAX_BUCKETS) cnt[tid] = 0;
   __syncthreads();
   const long long base = (long long)blockIdx.x * PART_TILE;
-#pragma unroll 4
+  // all loads of the thread are issued before the first use, so that their latencies overlap
+  typename DKey<KB>::Raw key[PART_ITEMS];
+#pragma unroll
+  for (int i = 0; i < PART_ITEMS; ++i) {
+    const long long e = base + (long long)i * PART_THREADS + tid;
+    if (e < n) key[i] = keys[e];
+  }
+#pragma unroll
   for (int i = 0; i < PART_ITEMS; ++i) {
     const long long e = base + (long long)i * PART_THREADS + tid;
     unsigned int b    = NO_BUCKET;
-    if (e < n) b = classify(ssplit, nbp - 1, DKey<KB>::okey(keys[e], xf), e);
+    if (e < n) b = classify(ssplit, nbp - 1, DKey<KB>::okey(key[i], xf), e);
     const unsigned int peers = __match_any_sync(0xFFFFFFFFu, b);
     if (b != NO_BUCKET && lane == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned int)__popc(peers));
   }
@@ -319,14 +327,17 @@ part_scatter_kernel(const typename DKey<KB>::Raw* __restrict__ keys, long long n
   unsigned int br[PART_ITEMS];  // bucket (bits 24..31) and rank among the warp's elements of that bucket
   unsigned int* my_cnt  = wcnt + warp * MAX_BUCKETS;
   const unsigned int lt = lanemask_lt();
+  // all loads of the thread are issued before the first use, so that their latencies overlap
+#pragma unroll
+  for (int i = 0; i < PART_ITEMS; ++i) {
+    const int e = stripe0 + 32 * i;
+    if (e < valid) key[i] = keys[base + e];
+  }
 #pragma unroll
   for (int i = 0; i < PART_ITEMS; ++i) {
     const int e    = stripe0 + 32 * i;
     unsigned int b = NO_BUCKET;
-    if (e < valid) {
-      key[i] = keys[base + e];
-      b      = classify(ssplit, nbp - 1, DKey<KB>::okey(key[i], xf), base + e);
-    }
+    if (e < valid) b = classify(ssplit, nbp - 1, DKey<KB>::okey(key[i], xf), base + e);
     const unsigned int peers = __match_any_sync(0xFFFFFFFFu, b);
     unsigned int old         = 0;
     if (b != NO_BUCKET) old = my_cnt[b];
@@ -504,9 +515,13 @@ struct PhaseTrace {
   explicit PhaseTrace(int rank)
     : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank),
       t0(std::chrono::steady_clock::now()) {}
-  void mark(const char* what)
+  // B2S_DIST_TRACE=sync (rank 0) / async... : "s" as second character waits for the stream first, so
+  // that the figures are device times per phase instead of enqueue times
+  void mark(const char* what, cudaStream_t stream = nullptr)
   {
     if (!on) return;
+    const char* e = std::getenv("B2S_DIST_TRACE");
+    if (e != nullptr && e[0] != 0 && e[1] == 's') cudaStreamSynchronize(stream);
     const auto t1 = std::chrono::steady_clock::now();
     if (used < (int)sizeof(line) - 1) {
       const int w = std::snprintf(line + used, sizeof(line) - used, " %s=%.2f", what,
@@ -804,8 +819,11 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   // status travels with the gathered blocks and all ranks return a failure together.
   Status st;
   const int nb  = nranks;
-  int nbp       = 1;
+  // up to 8 destinations and keys of at most 8 bytes: the register-counting partition kernels
+  const bool fast = nb <= FP_NB && kb <= 8;
+  int nbp         = 1;
   while (nbp < nb) nbp <<= 1;                       // padded bucket count
+  if (fast) nbp = FP_NB;
   const int S_all            = nranks * SAMPLES_PER_RANK;
   const long long ntiles     = (n + PART_TILE - 1) / PART_TILE;
   const long long capacity   = n + n / 8 + 65536;  // elements my receive buffers hold
@@ -821,6 +839,10 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   const size_t o_local = take(sizeof(LocalSplitter) * MAX_BUCKETS);
   const size_t o_counts = take(4 * (size_t)(ntiles > 0 ? ntiles : 1) * nbp), o_toff = take(8 * (size_t)(ntiles > 0 ? ntiles : 1) * nbp);
   const size_t o_totals = take(8 * MAX_BUCKETS), o_mineB = take(sizeof(BlockB)), o_allB = take(sizeof(BlockB) * nranks);
+  const long long nchunks = (ntiles + FP_CHUNK_TILES - 1) / FP_CHUNK_TILES;
+  // zeroed together: the partition kernels' status word and the per-chunk sums of the tile counts
+  const size_t zero_bytes = 256 + 8 * (size_t)FP_NB * (size_t)(nchunks > 0 ? nchunks : 1);
+  const size_t o_zero     = take(zero_bytes);
   size_t sample_ws_bytes = 0;
   b2s_workspace_bytes(B2S_UINT64, (size_t)S_all, (size_t)S_all, 1, &sample_ws_bytes);
   const size_t o_sws = take(sample_ws_bytes);
@@ -870,7 +892,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
                             cudaMemcpyDeviceToHost, stream));
   Event ev_hdr;
   if (ev_hdr.ev == nullptr) st.set(B2S_ERR_CUDA); else st.cuda(cudaEventRecord(ev_hdr.ev, stream));
-  trace.mark("samples");
+  trace.mark("samples", stream);
 
   // ---- splitters on the device: order the samples by (key, rank, position), weigh, pick ----
   Sample* d_samples     = reinterpret_cast<Sample*>(ctl + o_samples);
@@ -878,6 +900,9 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   unsigned int* d_counts = reinterpret_cast<unsigned int*>(ctl + o_counts);
   unsigned long long* d_toff = reinterpret_cast<unsigned long long*>(ctl + o_toff);
   long long* d_totals    = reinterpret_cast<long long*>(ctl + o_totals);
+  unsigned int* d_status = reinterpret_cast<unsigned int*>(ctl + (have_ctl ? o_zero : 0));
+  unsigned long long* d_chunks = reinterpret_cast<unsigned long long*>(ctl + o_zero + 256);
+  if (have_ctl) st.cuda(cudaMemsetAsync(ctl + o_zero, 0, zero_bytes, stream));
   if (have_ctl && st.ok()) {
     unsigned long long* khi = reinterpret_cast<unsigned long long*>(ctl + o_khi);
     unsigned long long* klo = reinterpret_cast<unsigned long long*>(ctl + o_klo);
@@ -915,16 +940,28 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     if (n > 0) {
       {
         prof::Scope ps(prof::K_DIST, stream);
-        by_width16(kb, [&](auto w) {
-          constexpr int KB = decltype(w)::value;
-          part_count_kernel<KB><<<(unsigned int)ntiles, PART_THREADS, 0, stream>>>(
-            static_cast<const typename DKey<KB>::Raw*>(keys_in), n, xf, d_local, nbp, d_counts);
-          return cudaSuccess;
-        });
+        if (fast) {
+          by_width(kb, [&](auto w) {
+            constexpr int KB = decltype(w)::value;
+            part_count_fast_kernel<KB><<<(unsigned int)ntiles, FP_THREADS, 0, stream>>>(
+              static_cast<const typename FpKey<KB>::Raw*>(keys_in), n, xf, d_local, d_counts, d_chunks);
+            return cudaSuccess;
+          });
+        } else {
+          by_width16(kb, [&](auto w) {
+            constexpr int KB = decltype(w)::value;
+            part_count_kernel<KB><<<(unsigned int)ntiles, PART_THREADS, 0, stream>>>(
+              static_cast<const typename DKey<KB>::Raw*>(keys_in), n, xf, d_local, nbp, d_counts);
+            return cudaSuccess;
+          });
+        }
       }
       {
         prof::Scope ps(prof::K_DIST, stream);
-        tile_scan_kernel<<<nbp, SCAN_THREADS, 0, stream>>>(d_counts, ntiles, nbp, d_toff, d_totals);
+        if (fast)
+          tile_scan_fast_kernel<<<(unsigned int)nchunks, FP_NB * 32, 0, stream>>>(d_counts, ntiles, d_chunks, d_toff, d_totals);
+        else
+          tile_scan_kernel<<<nbp, SCAN_THREADS, 0, stream>>>(d_counts, ntiles, nbp, d_toff, d_totals);
       }
     } else {
       st.cuda(cudaMemsetAsync(d_totals, 0, 8 * MAX_BUCKETS, stream));
@@ -957,7 +994,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
       peer_pay[p]  = argsort ? pbase + r.off[1] : nullptr;
     }
   }
-  trace.mark("map");
+  trace.mark("map", stream);
 
   // ---- second all-gather: counts per destination, mapping flag, status ----
   BlockB* d_mineB = reinterpret_cast<BlockB*>(ctl + (have_ctl ? o_mineB : 0));
@@ -1070,7 +1107,29 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     for (int p = 0; p < nranks; ++p)
       if (flags[p * (sizeof(BlockB) / 8)] != B2S_OK) return (int)flags[p * (sizeof(BlockB) / 8)];
   }
-  if (n > 0) {
+  if (n > 0 && fast) {
+    prof::Scope ps(prof::K_XCHG, stream);
+    FpDst fd{};
+    for (int d = 0; d < nranks; ++d) {
+      fd.keys[d] = dst.keys[d];
+      fd.pay[d]  = dst.pay[d];
+    }
+    by_width(kb, [&](auto w) {
+      constexpr int KB = decltype(w)::value;
+      using Raw        = typename FpKey<KB>::Raw;
+      auto launch = [&](auto kern, size_t bytes) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+        kern<<<(unsigned int)ntiles, FP_THREADS, bytes, stream>>>(static_cast<const Raw*>(keys_in), n, xf, d_local, d_toff, fd,
+                                                                    (long long)global_offset, gmin, d_status);
+        return cudaGetLastError();
+      };
+      if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0>, FpSmem<KB, 0>::BYTES);
+      if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4>, FpSmem<KB, 4>::BYTES);
+      return launch(part_scatter_fast_kernel<KB, 8>, FpSmem<KB, 8>::BYTES);
+    });
+    st.cuda(cudaGetLastError());
+  } else if (n > 0) {
     prof::Scope ps(prof::K_XCHG, stream);
     by_width16(kb, [&](auto w) {
       constexpr int KB = decltype(w)::value;
@@ -1119,7 +1178,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
       prof::end(prof::K_XCHG, stream);
     }
   }
-  trace.mark("partition");
+  trace.mark("partition", stream);
 
   // ---- sort what I received ----
   void* result = mem.get((size_t)(n_recv > 0 ? n_recv : 1) * out_elem);
@@ -1157,10 +1216,13 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
       }
     }
   }
-  // temporaries are handed back only once the stream is done with them; a wait inside the local
-  // sort that ran out shows up here
+  // temporaries are handed back only once the stream is done with them; a bounded wait that ran
+  // out inside the partition kernel or the local sort shows up here
+  unsigned int part_status = 0;
+  st.cuda(cudaMemcpyAsync(&part_status, d_status, sizeof(part_status), cudaMemcpyDeviceToHost, stream));
   if (sort_ws != nullptr && st.ok() && dtype != B2S_COMPLEX128) st.set(b2s_check_status(sort_ws, stream));
   else st.cuda(cudaStreamSynchronize(stream));
+  if (part_status != 0) st.set((int)part_status);
   trace.mark("sort(sync)");
   if (!st.ok()) return st.code;
   mem.disown(result);
