@@ -5,6 +5,9 @@
 #include "b2s_prof.h"
 #include "b2s_radix.cuh"
 #include "b2s_segsort.cuh"
+#include "b2s_segmerge.cuh"
+
+#include <cstdlib>
 
 namespace b2s {
 
@@ -284,10 +287,54 @@ inline cudaError_t segsort_cfg(int xf, const void* in, void* out, int64_t* idx_o
   return cudaGetLastError();
 }
 
+// The merge-sort form of the on-chip row sort (4- and 8-byte keys, rows of more than 256 elements).
+template <int KB, bool PAIRS, int THREADS>
+inline cudaError_t segmerge_cfg(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
+                                unsigned long long nseg, int64_t index_offset, cudaStream_t stream)
+{
+  using K   = typename KeyOf<KB>::type;
+  using S   = SegMergeSmem<KB, PAIRS, THREADS>;
+  auto kern = segmerge_kernel<KB, PAIRS, THREADS>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::BYTES);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  int per_sm = 1;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THREADS, S::BYTES);
+  if (per_sm < 1) per_sm = 1;
+  unsigned long long grid = (unsigned long long)sms * per_sm;
+  if (grid > nseg) grid = nseg;
+  {
+    prof::Scope ps(prof::K_SEGSORT, stream);
+    kern<<<(unsigned int)grid, THREADS, S::BYTES, stream>>>(static_cast<const K*>(in), static_cast<K*>(out), idx_out, seg_len,
+                                                             nseg, xf, index_offset);
+  }
+  return cudaGetLastError();
+}
+
+inline bool seg_merge_enabled()
+{
+  const char* e = std::getenv("B2S_SEG_MERGE");  // 0: keep every row on the radix kernel (comparisons)
+  return e == nullptr || e[0] != '0';
+}
+
 template <int KB, bool PAIRS>
 inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx_out, unsigned int seg_len,
                                  unsigned long long nseg, int64_t index_offset, Ctrl* ctrl, cudaStream_t stream)
 {
+  if constexpr (KB == 4 || KB == 8) {
+    // keys of a sort are mapped back from their images, which the complex64 image does not allow
+    if (seg_len > 256 && (PAIRS || xf != XF_CFLOAT) && seg_merge_enabled()) {
+      constexpr int V = SM_VT;
+      if (seg_len <= 32 * V) return segmerge_cfg<KB, PAIRS, 32>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+      if (seg_len <= 64 * V) return segmerge_cfg<KB, PAIRS, 64>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+      if (seg_len <= 128 * V) return segmerge_cfg<KB, PAIRS, 128>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+      if (seg_len <= 256 * V) return segmerge_cfg<KB, PAIRS, 256>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+      if (seg_len <= 512 * V) return segmerge_cfg<KB, PAIRS, 512>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+      if constexpr (V == 8) return segmerge_cfg<KB, PAIRS, 1024>(xf, in, out, idx_out, seg_len, nseg, index_offset, stream);
+    }
+  }
   if (seg_len <= 128) return segsort_cfg<KB, PAIRS, 32, 4>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
   if (seg_len <= 1024) return segsort_cfg<KB, PAIRS, 128, 8>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
   if (seg_len <= 4096) return segsort_cfg<KB, PAIRS, 256, 16>(xf, in, out, idx_out, seg_len, nseg, index_offset, ctrl, stream);
