@@ -135,7 +135,8 @@ struct Ctrl {
   unsigned int status;                  // 0 or a b2s_status_t, written by kernels
   unsigned int abort;                   // set with status; every later wait gives up at once
   unsigned int tile_counter[MAX_PASSES];
-  unsigned int pad_[6];
+  unsigned int hist_done;               // CTAs of the histogram kernel that have added their counts
+  unsigned int pad_[5];
   unsigned int hist[MAX_PASSES][RADIX]; // digit counts, then (after the scan kernel) exclusive bases
   PassDesc pass[MAX_PASSES];
   FixDesc fix;

@@ -130,10 +130,6 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   const unsigned int per_cta = HIST_THREADS * 16;
   unsigned int hgrid         = (n + per_cta - 1) / per_cta;
   if (hgrid > (unsigned int)sms * 4) hgrid = sms * 4;
-  {
-    prof::Scope ps(prof::K_HIST, stream);
-    hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl);
-  }
   RouteArgs ra{};
   ra.keys_in     = in;
   ra.keys_out    = out;
@@ -148,8 +144,9 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.npass       = KB;
   ra.key_bytes   = KB;
   {
-    prof::Scope ps(prof::K_SCAN, stream);
-    scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
+    // digit histograms of all passes; the CTA that finishes last scans them and routes the passes
+    prof::Scope ps(prof::K_HIST, stream);
+    hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl, ra);
   }
   const SegGeom geo{n, lay.tiles, 1u, KB, nullptr};
   e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, geo, index_offset, stream)
@@ -232,11 +229,13 @@ inline cudaError_t radix_seg_xf(const void* in, void* out, int64_t* idx_out, uns
     prof::Scope ps(prof::K_SCAN, stream);
     scan_route_kernel<<<1, RADIX, 0, stream>>>(ctrl, ra);
   }
+  // every pass is active here (empty global histogram), so the only leftover is the copy of an
+  // in-place single-pass sort out of its temporary
   const SegGeom geo{seg_len, lay.tiles_per_seg, nseg, KB, sh};
   e = pairs ? launch_sweeps<KB, XF, true>(ctrl, lb, lay.tiles, geo, index_offset, stream)
             : launch_sweeps<KB, XF, false>(ctrl, lb, lay.tiles, geo, index_offset, stream);
   if (e != cudaSuccess) return e;
-  {
+  if (out != nullptr && out == in) {
     prof::Scope ps(prof::K_FIXUP, stream);
     fixup_kernel<<<148 * 4, 256, 0, stream>>>(ctrl, seg_len * nseg, index_offset);
   }

@@ -10,76 +10,6 @@
 namespace b2s {
 
 // ---------------------------------------------------------------------------------------------
-// Kernel 1: digit histograms of every pass in one read of the keys.
-// Warp-level shortcut: when all 32 lanes hold the same digit (sorted input, constant high
-// bytes) one lane adds 32 instead of 32 serialised shared-memory atomics.
-// ---------------------------------------------------------------------------------------------
-#ifndef B2S_HIST_FORM
-#define B2S_HIST_FORM 0
-#endif
-template <int KB, int XF>
-__device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], typename KeyOf<KB>::type raw)
-{
-  const auto k = to_ordered<KB, XF>(raw);
-#pragma unroll
-  for (int p = 0; p < KB; ++p) {
-    const unsigned int d = (unsigned int)(k >> (8 * p)) & 0xFFu;
-#if B2S_HIST_FORM == 1
-    const int same = __all_sync(0xFFFFFFFFu, __shfl_sync(0xFFFFFFFFu, d, 0) == d);
-#elif B2S_HIST_FORM == 2
-    const int same = 0;
-#else
-    int same;
-    __match_all_sync(0xFFFFFFFFu, d, &same);
-#endif
-    if (same) {
-      if ((threadIdx.x & 31) == 0) atomicAdd(&sh[p][d], 32u);
-    } else {
-      atomicAdd(&sh[p][d], 1u);
-    }
-  }
-}
-
-constexpr int HIST_THREADS = 512;
-
-template <int KB, int XF>
-__global__ void __launch_bounds__(HIST_THREADS)
-hist_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int n, Ctrl* ctrl)
-{
-  using K = typename KeyOf<KB>::type;
-  __shared__ unsigned int sh[KB][RADIX];
-  for (int i = threadIdx.x; i < KB * RADIX; i += HIST_THREADS) (&sh[0][0])[i] = 0;
-  __syncthreads();
-
-  constexpr int VEC = 16 / KB;  // keys per 128-bit load
-  const bool aligned = (reinterpret_cast<uintptr_t>(keys) & 15u) == 0;
-  const unsigned int nvec = aligned ? n / VEC : 0;
-  // Round the vector count down to whole warps so that the warp shortcut sees 32 live lanes.
-  const unsigned int nvec_w  = nvec & ~31u;
-  const unsigned int gthread = blockIdx.x * HIST_THREADS + threadIdx.x;
-  const unsigned int gstride = gridDim.x * HIST_THREADS;
-  const uint4* vkeys         = reinterpret_cast<const uint4*>(keys);
-  for (unsigned int v = gthread; v < nvec_w; v += gstride) {
-    const uint4 q = __ldg(vkeys + v);
-    alignas(16) K tmp[VEC];
-    *reinterpret_cast<uint4*>(tmp) = q;
-#pragma unroll
-    for (int j = 0; j < VEC; ++j) hist_add_full_warp<KB, XF>(sh, tmp[j]);
-  }
-  // remainder: plain atomics
-  for (unsigned int i = nvec_w * VEC + gthread; i < n; i += gstride) {
-    const auto k = to_ordered<KB, XF>(keys[i]);
-#pragma unroll
-    for (int p = 0; p < KB; ++p) atomicAdd(&sh[p][(unsigned int)(k >> (8 * p)) & 0xFFu], 1u);
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < KB * RADIX; i += HIST_THREADS) {
-    const unsigned int c = (&sh[0][0])[i];
-    if (c) atomicAdd(&ctrl->hist[0][0] + i, c);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
 // Kernel 2 (one CTA): turn the histograms into exclusive digit bases, find passes whose digit is
 // constant over the array (a stable pass over a constant digit is the identity, so it is
 // skipped) and route the remaining passes through the two temporaries so that the last one
@@ -98,26 +28,31 @@ struct RouteArgs {
   int key_bytes;
 };
 
-static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, RouteArgs a)
+// Body of the scan-and-route step, run by one whole CTA of at least RADIX threads (threads beyond
+// the first RADIX only take part in the barriers).
+__device__ __forceinline__ void scan_route_body(Ctrl* ctrl, const RouteArgs& a)
 {
   __shared__ unsigned int warp_tot[RADIX / 32];
   __shared__ int active[MAX_PASSES];
   const int d    = threadIdx.x;
+  const bool on  = d < RADIX;
   const int lane = d & 31, w = d >> 5;
   for (int p = 0; p < a.npass; ++p) {
-    const unsigned int c = ctrl->hist[p][d];
-    const int constant   = __syncthreads_or(c == a.n);
+    const unsigned int c = on ? ctrl->hist[p][d] : 0u;
+    const int constant   = __syncthreads_or(on && c == a.n);
     unsigned int incl    = c;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
       if (lane >= o) incl += t;
     }
-    if (lane == 31) warp_tot[w] = incl;
+    if (on && lane == 31) warp_tot[w] = incl;
     __syncthreads();
-    unsigned int base = 0;
-    for (int i = 0; i < w; ++i) base += warp_tot[i];
-    ctrl->hist[p][d] = base + incl - c;
+    if (on) {
+      unsigned int base = 0;
+      for (int i = 0; i < w; ++i) base += warp_tot[i];
+      ctrl->hist[p][d] = base + incl - c;
+    }
     if (d == 0) active[p] = !constant;
     __syncthreads();
   }
@@ -169,6 +104,88 @@ static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, Ro
     fix.widen_src   = a.idx_in;
   }
   ctrl->fix = fix;
+}
+
+static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, RouteArgs a) { scan_route_body(ctrl, a); }
+
+// ---------------------------------------------------------------------------------------------
+// Kernel 1: digit histograms of every pass in one read of the keys.
+// Warp-level shortcut: when all 32 lanes hold the same digit (sorted input, constant high
+// bytes) one lane adds 32 instead of 32 serialised shared-memory atomics.
+// ---------------------------------------------------------------------------------------------
+#ifndef B2S_HIST_FORM
+#define B2S_HIST_FORM 0
+#endif
+template <int KB, int XF>
+__device__ __forceinline__ void hist_add_full_warp(unsigned int (*sh)[RADIX], typename KeyOf<KB>::type raw)
+{
+  const auto k = to_ordered<KB, XF>(raw);
+#pragma unroll
+  for (int p = 0; p < KB; ++p) {
+    const unsigned int d = (unsigned int)(k >> (8 * p)) & 0xFFu;
+#if B2S_HIST_FORM == 1
+    const int same = __all_sync(0xFFFFFFFFu, __shfl_sync(0xFFFFFFFFu, d, 0) == d);
+#elif B2S_HIST_FORM == 2
+    const int same = 0;
+#else
+    int same;
+    __match_all_sync(0xFFFFFFFFu, d, &same);
+#endif
+    if (same) {
+      if ((threadIdx.x & 31) == 0) atomicAdd(&sh[p][d], 32u);
+    } else {
+      atomicAdd(&sh[p][d], 1u);
+    }
+  }
+}
+
+constexpr int HIST_THREADS = 512;
+
+template <int KB, int XF>
+__global__ void __launch_bounds__(HIST_THREADS)
+hist_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int n, Ctrl* ctrl, RouteArgs route)
+{
+  using K = typename KeyOf<KB>::type;
+  __shared__ unsigned int sh[KB][RADIX];
+  for (int i = threadIdx.x; i < KB * RADIX; i += HIST_THREADS) (&sh[0][0])[i] = 0;
+  __syncthreads();
+
+  constexpr int VEC = 16 / KB;  // keys per 128-bit load
+  const bool aligned = (reinterpret_cast<uintptr_t>(keys) & 15u) == 0;
+  const unsigned int nvec = aligned ? n / VEC : 0;
+  // Round the vector count down to whole warps so that the warp shortcut sees 32 live lanes.
+  const unsigned int nvec_w  = nvec & ~31u;
+  const unsigned int gthread = blockIdx.x * HIST_THREADS + threadIdx.x;
+  const unsigned int gstride = gridDim.x * HIST_THREADS;
+  const uint4* vkeys         = reinterpret_cast<const uint4*>(keys);
+  for (unsigned int v = gthread; v < nvec_w; v += gstride) {
+    const uint4 q = __ldg(vkeys + v);
+    alignas(16) K tmp[VEC];
+    *reinterpret_cast<uint4*>(tmp) = q;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) hist_add_full_warp<KB, XF>(sh, tmp[j]);
+  }
+  // remainder: plain atomics
+  for (unsigned int i = nvec_w * VEC + gthread; i < n; i += gstride) {
+    const auto k = to_ordered<KB, XF>(keys[i]);
+#pragma unroll
+    for (int p = 0; p < KB; ++p) atomicAdd(&sh[p][(unsigned int)(k >> (8 * p)) & 0xFFu], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < KB * RADIX; i += HIST_THREADS) {
+    const unsigned int c = (&sh[0][0])[i];
+    if (c) atomicAdd(&ctrl->hist[0][0] + i, c);
+  }
+  // The CTA that finishes last turns the complete histograms into digit bases and routes the
+  // passes (what would otherwise be a launch of its own).
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&ctrl->hist_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  scan_route_body(ctrl, route);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -225,11 +242,8 @@ static __global__ void __launch_bounds__(RADIX) seg_scan_kernel(unsigned int* __
 // ---------------------------------------------------------------------------------------------
 // Kernel 4: the rare leftovers described by FixDesc.
 // ---------------------------------------------------------------------------------------------
-static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, unsigned int n, int64_t index_offset)
+__device__ __forceinline__ void fixup_body(const FixDesc& f, unsigned int n, int64_t index_offset, size_t gthread, size_t gstride)
 {
-  const FixDesc f         = ctrl->fix;
-  const size_t gthread    = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t gstride    = (size_t)gridDim.x * blockDim.x;
   if (f.copy_src != nullptr) {
     const unsigned char* s = static_cast<const unsigned char*>(f.copy_src);
     unsigned char* d       = static_cast<unsigned char*>(f.copy_dst);
@@ -254,6 +268,14 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
   }
 }
 
+// The rare leftovers: the copy of an in-place single-pass sort out of its temporary; keys that are
+// all equal (no pass runs: copy, synthesised indices).  A launch of its own: as a call inside the
+// radix pass it cost the keys-only passes 5 % (measured), far more than the launch.
+static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, unsigned int n, int64_t index_offset)
+{
+  fixup_body(ctrl->fix, n, index_offset, (size_t)blockIdx.x * blockDim.x + threadIdx.x, (size_t)gridDim.x * blockDim.x);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel 3: one onesweep pass.  A CTA takes the next tile (ticket from an atomic counter, so
 // every predecessor of a tile is already running or done), ranks its keys stably by the pass's
@@ -271,6 +293,11 @@ static __global__ void __launch_bounds__(256) fixup_kernel(const Ctrl* ctrl, uns
 // ---------------------------------------------------------------------------------------------
 #ifndef B2S_RANK_ATOMIC
 #define B2S_RANK_ATOMIC 0
+#endif
+// 0: two lookups per key in the permutation; 1: digit starts folded into the row prefixes;
+// 2: folded for key + index passes of keys up to 4 bytes only (measured: a gain there, a loss elsewhere)
+#ifndef B2S_FOLD_EXCL
+#define B2S_FOLD_EXCL 2
 #endif
 constexpr unsigned int LB_FLAG_AGG  = 1u << 30;  // tile count published
 constexpr unsigned int LB_FLAG_INCL = 2u << 30;  // inclusive prefix published
@@ -342,8 +369,9 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 
   if (tid == 0) {
     // one thread reads the abort flag for the whole CTA, so that all of its threads leave together
+    const unsigned int ticket = atomicAdd(&ctrl->tile_counter[pass], 1u);
     misc[1] = ld_relaxed(&ctrl->abort);
-    misc[0] = atomicAdd(&ctrl->tile_counter[pass], 1u);
+    misc[0] = ticket;
     mbar_init(bar, 1);
     fence_mbar_init();
   }
@@ -448,14 +476,18 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
 #endif
   __syncthreads();
 
-  // ---- per-digit tile counts: exclusive scan over counter rows, then over digits ----
+  // ---- per-digit tile counts: exclusive scan over the counter rows, then over the digits.  FOLD:
+  // a second sweep over the rows adds the digit's start to every row's prefix, so that the
+  // permutation below needs one table lookup per key instead of two (pays for the larger tiles of
+  // the key + index passes; the keys-only tiles are too small to win it back) ----
+  constexpr bool FOLD = B2S_FOLD_EXCL == 1 || (B2S_FOLD_EXCL == 2 && PAIRS && KB <= 4);
   unsigned int my_count = 0;
   if (tid < RADIX) {
     unsigned int run = 0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       const unsigned int t  = hist[r * RADIX + tid];
-      hist[r * RADIX + tid] = run;
+      if (!FOLD) hist[r * RADIX + tid] = run;
       run += t;
     }
     my_count = run;
@@ -474,6 +506,15 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
     unsigned int add = 0;
     for (int w = 0; w < warp; ++w) add += base_ml[w];
     my_excl_tile = dig_excl[tid] + add;
+    if (FOLD) {
+      unsigned int run = my_excl_tile;
+#pragma unroll 1
+      for (int r = 0; r < ROWS; ++r) {
+        const unsigned int t  = hist[r * RADIX + tid];
+        hist[r * RADIX + tid] = run;
+        run += t;
+      }
+    }
   }
   __syncthreads();
 
@@ -483,17 +524,17 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
   // published too and the walk rarely has to poll.
   unsigned int* mine = lookback + (size_t)tile * RADIX + (tid < RADIX ? tid : 0);
   if (tid < RADIX) {
-    dig_excl[tid] = my_excl_tile;
+    if (!FOLD) dig_excl[tid] = my_excl_tile;
     st_relaxed(mine, (t_in == 0 ? LB_FLAG_INCL : LB_FLAG_AGG) | my_count);
   }
-  __syncthreads();
+  if (!FOLD) __syncthreads();
 
   // ---- permute the tile inside shared memory: position = digit start + earlier rows + rank ----
   unsigned int pos[ITEMS];
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     const unsigned int d = rd[i] >> 16;
-    pos[i]               = dig_excl[d] + my_hist[(i / IPC) * RADIX + d] + (rd[i] & 0xFFFFu);
+    pos[i]               = (FOLD ? 0u : dig_excl[d]) + my_hist[(i / IPC) * RADIX + d] + (rd[i] & 0xFFFFu);
     stage_keys[pos[i]]   = key[i];
   }
   if (PAIRS) {
