@@ -107,3 +107,22 @@ def rebalance_1d(part: torch.Tensor, part_start: int, out: torch.Tensor, out_sta
                                    ctypes.cast(pool.alloc_cb, ctypes.c_void_p), ctypes.cast(pool.free_cb, ctypes.c_void_p),
                                    None, None, None, runtime.stream_handle())
     _lib.check(st, "b2s_dist_rebalance_1d")
+
+
+def dist_sort_nd(tile: torch.Tensor, argsort: bool) -> torch.Tensor:
+    """Sorts an N-D tile along its last axis when that axis is the one split over the processes
+    (every process holds the same rows and a slice of each): all rows in one call, results in the
+    tile's own extents."""
+    lib = _lib.lib()
+    assert tile.is_cuda and tile.is_contiguous() and tile.ndim >= 2
+    np_dtype = to_numpy_dtype(tile.dtype)
+    extent = tile.shape[-1]
+    rows = tile.numel() // extent if extent else 0
+    out = torch.empty(tile.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
+    pool = _Pool()
+    st = lib.b2s_dist_sort_nd(_lib.DTYPE_CODE[np_dtype], tile.data_ptr() if tile.numel() else None,
+                              out.data_ptr() if out.numel() else None, int(argsort), rows, extent, nccl_comm(), dist.get_rank(),
+                              dist.get_world_size(), ctypes.cast(pool.alloc_cb, ctypes.c_void_p),
+                              ctypes.cast(pool.free_cb, ctypes.c_void_p), None, None, None, runtime.stream_handle())
+    _lib.check(st, "b2s_dist_sort_nd")
+    return out

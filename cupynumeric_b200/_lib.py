@@ -105,6 +105,12 @@ SIGNATURES = {
                                    ctypes.POINTER(_P), ctypes.POINTER(_SZ), ctypes.POINTER(_I64), _P]),
     "b2s_dist_rebalance_1d": (_I, [_SZ, _P, _SZ, _I64, _P, _SZ, _I64, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
     "b2s_dist_rebalance_1d_ops": (_I, [_SZ, _P, _SZ, _I64, _P, _SZ, _I64, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "b2s_dist_sort_nd_ops": (_I, [_I, _P, _P, _I, _SZ, _SZ, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "b2s_dist_sort_nd": (_I, [_I, _P, _P, _I, _SZ, _SZ, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "b2s_partition_workspace_bytes": (_I, [ctypes.POINTER(_SZ)]),
+    "b2s_partition_1d": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _P, _SZ, _P]),
+    "b2s_lexsort_workspace_bytes": (_I, [_I, _P, _SZ, _SZ, ctypes.POINTER(_SZ)]),
+    "b2s_lexsort": (_I, [_I, _P, _P, _P, _SZ, _SZ, _P, _SZ, _P]),
     "b2s_nccl_comm_ops": (_I, [_P, _P, _I, _I, _P]),
     "b2s_nccl_comm_ops_release": (None, [_P]),
     "b2s_thread_comm_create": (_I, [_I, _P]),

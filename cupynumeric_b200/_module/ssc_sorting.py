@@ -81,10 +81,44 @@ def _check_kth(kth: Any, extent: int) -> None:
             raise ValueError(f"kth(={k}) out of bounds ({extent})")
 
 
+# 1-D tiles longer than this take the selection kernels; shorter ones (and rows of N-D arrays,
+# which the on-chip row sort handles at one read and one write) are simply sorted
+SELECT_MIN = 8192
+
+
+def _select_1d(a: ndarray, kth: Any, want_indices: bool):
+    """Radix select + three-block partition of a 1-D array held by one process (``b2s_partition_1d``).
+    Returns None when the case is not the selection's (several kth values, short or distributed array)."""
+    import ctypes
+
+    import torch
+
+    from .. import _lib
+    from ..runtime import runtime
+
+    ks = np.atleast_1d(np.asarray(kth))
+    if a.ndim != 1 or ks.size != 1 or a.size <= SELECT_MIN or runtime.num_procs > 1 or a.dtype == np.complex128:
+        return None
+    k = int(ks[0]) % a.size
+    lib = _lib.lib()
+    tile = a.torch().contiguous()
+    out = torch.empty(tile.shape, dtype=torch.int64 if want_indices else tile.dtype, device=tile.device)
+    need = ctypes.c_size_t()
+    _lib.check(lib.b2s_partition_workspace_bytes(ctypes.byref(need)), "b2s_partition_workspace_bytes")
+    ws = torch.empty(need.value, dtype=torch.uint8, device=tile.device)   # not the sorts' workspace: other contents
+    st = lib.b2s_partition_1d(_lib.DTYPE_CODE[a.dtype], tile.data_ptr(), None if want_indices else out.data_ptr(),
+                              out.data_ptr() if want_indices else None, tile.numel(), k, 0, ws.data_ptr(), ws.numel(),
+                              runtime.stream_handle())
+    _lib.check(st, "b2s_partition_1d")
+    return array(out)
+
+
 def partition(a: Any, kth: Any, axis: int | None = -1, kind: str = "introselect", order: Any = None) -> ndarray:
-    """A partitioned copy of ``a``.  Like the reference, which "falls back to sort for now"
-    (``cupynumeric/_thunk/deferred.py:5476-5494``), the result is fully sorted along ``axis``,
-    which satisfies the partition property for every ``kth``."""
+    """A partitioned copy of ``a``: the element of rank ``kth`` along ``axis`` is where a sort would
+    put it, smaller elements come before it, larger ones after.  Long 1-D arrays go through a
+    radix select (O(n) bytes); every other case is sorted along ``axis``, as the reference does for
+    all of them ("falls back to sort for now", ``cupynumeric/_thunk/deferred.py:5476-5494``) - a
+    sorted array satisfies the partition property for every ``kth``."""
     a = array(a)
     if order is not None:
         raise NotImplementedError(
@@ -93,11 +127,13 @@ def partition(a: Any, kth: Any, axis: int | None = -1, kind: str = "introselect"
         if axis >= a.ndim or axis < -a.ndim:
             raise ValueError("invalid axis")
         _check_kth(kth, a.shape[axis])
-    return sort(a, axis=axis)
+    flat = a if axis is not None or a.ndim <= 1 else array(a.torch().reshape(-1))
+    selected = _select_1d(flat, kth, False) if (axis is None or a.ndim == 1) else None
+    return selected if selected is not None else sort(a, axis=axis)
 
 
 def argpartition(a: Any, kth: Any, axis: int | None = -1, kind: str = "introselect", order: Any = None) -> ndarray:
-    """Indices that partition ``a``; the full argsort, as in the reference."""
+    """Indices that partition ``a`` (see ``partition``); the full argsort where selection does not apply."""
     a = array(a)
     if order is not None:
         raise NotImplementedError(
@@ -106,17 +142,23 @@ def argpartition(a: Any, kth: Any, axis: int | None = -1, kind: str = "introsele
         if axis >= a.ndim or axis < -a.ndim:
             raise ValueError("invalid axis")
         _check_kth(kth, a.shape[axis])
-    return argsort(a, axis=axis)
+    flat = a if axis is not None or a.ndim <= 1 else array(a.torch().reshape(-1))
+    selected = _select_1d(flat, kth, True) if (axis is None or a.ndim == 1) else None
+    return selected if selected is not None else argsort(a, axis=axis)
 
 
 def lexsort(keys: Any, axis: int | None = -1) -> ndarray:
-    """Stable lexicographic argsort over several keys, the last key being the most significant:
-    one stable argsort per key, each applied to the key reordered by the indices so far
-    (``cupynumeric/_module/ssc_sorting.py:423-444``).  The reference first replaces NaN and
-    infinities by finite stand-ins (``:354-421``); that is not needed here because the sort
-    itself orders -inf < finite < +inf < NaN.  Single process only."""
+    """Stable lexicographic argsort over several keys, the last key being the most significant
+    (``cupynumeric/_module/ssc_sorting.py:354-444``).  One call into the library
+    (``b2s_lexsort``): a stable radix argsort per key with the order so far carried through it; the
+    reference chains ARGSORT tasks and gathers from Python and first replaces NaN and infinities by
+    finite stand-ins, which is not needed here because the sort itself orders
+    -inf < finite < +inf < NaN.  Single process only."""
+    import ctypes
+
     import torch
 
+    from .. import _lib
     from ..runtime import runtime
 
     if keys is None:
@@ -137,9 +179,22 @@ def lexsort(keys: Any, axis: int | None = -1) -> ndarray:
         return array(np.zeros((), dtype=np.int64))
     if klist[0].size == 0:
         return array(np.empty(first_shape, dtype=np.int64))
-    indices = argsort(klist[0], axis=axis, kind="stable").torch()
-    for key in klist[1:]:
-        reordered = torch.take_along_dim(key.torch(), indices, dim=axis)
-        order = argsort(array(reordered), axis=axis, kind="stable").torch()
-        indices = torch.take_along_dim(indices, order, dim=axis)
-    return array(indices)
+    ndim = klist[0].ndim
+    if axis >= ndim or axis < -ndim:
+        raise ValueError("invalid axis")
+    axis %= ndim
+    # the sort axis last, dense (a no-op for the usual axis=-1 on contiguous keys)
+    tiles = [k.torch().movedim(axis, -1).contiguous() for k in klist]
+    shape = tiles[0].shape
+    volume, segment = tiles[0].numel(), shape[-1]
+    lib = _lib.lib()
+    n = len(tiles)
+    codes = (ctypes.c_int * n)(*[_lib.DTYPE_CODE[k.dtype] for k in klist])
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in tiles])
+    need = ctypes.c_size_t()
+    _lib.check(lib.b2s_lexsort_workspace_bytes(n, codes, volume, segment, ctypes.byref(need)), "b2s_lexsort_workspace_bytes")
+    ws = torch.empty(max(need.value, 256), dtype=torch.uint8, device=tiles[0].device)
+    out = torch.empty(shape, dtype=torch.int64, device=tiles[0].device)
+    _lib.check(lib.b2s_lexsort(n, codes, ptrs, out.data_ptr(), volume, segment, ws.data_ptr(), ws.numel(),
+                               runtime.stream_handle()), "b2s_lexsort")
+    return array(out.movedim(-1, axis).contiguous() if axis != ndim - 1 else out)

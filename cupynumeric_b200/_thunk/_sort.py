@@ -102,20 +102,25 @@ def sort_task(output: DeferredArray, input: DeferredArray, argsort: bool, stable
 
 
 def sort_split_axis(output: DeferredArray, input: DeferredArray, tile: torch.Tensor, argsort: bool) -> None:
-    """N-D tile whose sort (last) axis is the one split over the processes: every segment is a
-    1-D array spanning the ranks.  Each segment goes through the distributed 1-D sort and is then
-    moved back into this rank's fixed extent, because the output store is bound and aligned with
-    the input (the reference: sample_sort_nccl_nd + rebalance_data,
-    ``src/cupynumeric/sort/sort.cu:1759-1773,799-1261``).  One segment at a time: meant for the
-    few long segments such a tiling produces, not for many short ones."""
-    from .._dist import dist_sort_1d, rebalance_1d
+    """N-D tile whose sort (last) axis is the one split over the processes: every row is a 1-D
+    array spanning the ranks, and the output store is bound and aligned with the input, so every
+    rank must end up with exactly its own extent of every sorted row (the reference:
+    sample_sort_nccl_nd over all segments + rebalance_data,
+    ``src/cupynumeric/sort/sort.cu:1759-1773,799-1261``).  With at least as many rows as ranks all
+    rows go through one call (``b2s_dist_sort_nd``: rows dealt out, completed by one exchange,
+    sorted, returned by another).  Fewer rows than ranks would leave ranks idle that way: each row
+    then takes the distributed 1-D sort and is moved back into this rank's extent."""
+    from .._dist import dist_sort_1d, dist_sort_nd, rebalance_1d
 
     extent = tile.shape[-1]
     rows = tile.reshape(-1, extent)
-    out = torch.empty(rows.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
-    for i in range(rows.shape[0]):
-        part, start = dist_sort_1d(rows[i], argsort, input.global_lo)
-        rebalance_1d(part, start, out[i], input.global_lo)
+    if rows.shape[0] >= runtime.num_procs:
+        out = dist_sort_nd(rows, argsort)
+    else:
+        out = torch.empty(rows.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
+        for i in range(rows.shape[0]):
+            part, start = dist_sort_1d(rows[i], argsort, input.global_lo)
+            rebalance_1d(part, start, out[i], input.global_lo)
     output.base = out.reshape(tile.shape)
     output.global_lo, output.tiled_axis = input.global_lo, input.tiled_axis
 

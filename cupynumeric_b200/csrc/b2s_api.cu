@@ -147,22 +147,24 @@ inline int chunk_layout(int dtype, int kb, size_t n, bool argsort, ChunkLayout* 
 // Sizes the single radix sort takes with 32-bit payloads carried through its passes.
 bool local_sort_pos32_supported(size_t n) { return n > SEG_CAP && n < single_sort_limit(); }
 
-// Stable 1-D argsort of keys that already carry a 32-bit payload each (pay_in[i] belongs to
-// keys_in[i]): idx_out[k] = index_offset + payload of the k-th smallest key.  The distributed sort
-// uses it on what a rank received: the payload is the element's global position minus a common
-// base, and travelling as 32 bits it costs the radix passes no more than a plain argsort.
+// Stable 1-D argsort of keys that carry a 32-bit payload each (pay_in[i] belongs to keys_in[i];
+// null: the payload of element i is i).  out32 == 0: idx_out[k] = index_offset + payload of the
+// k-th smallest key, as int64; out32 != 0: idx_out points to n uint32 values that receive the bare
+// payloads.  The distributed sort uses it on what a rank received (payload = global position minus a
+// common base), the lexicographic sort to carry its order from key to key: travelling as 32 bits the
+// payload costs the radix passes no more than a plain argsort.
 int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
-                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream)
+                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, int out32)
 {
   DtypeInfo di;
   if (!dtype_info(dtype, &di) || !local_sort_pos32_supported(n)) return B2S_ERR_UNSUPPORTED;
-  if (keys_in == nullptr || pay_in == nullptr || idx_out == nullptr) return B2S_ERR_INVALID_ARG;
+  if (keys_in == nullptr || idx_out == nullptr) return B2S_ERR_INVALID_ARG;
   size_t need = 0;
   int rc      = b2s_workspace_bytes(dtype, n, n, 1, &need);
   if (rc != B2S_OK) return rc;
   if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
   const cudaError_t e = radix_any(di.kb, di.xf, keys_in, nullptr, idx_out, (unsigned int)n, index_offset,
-                                  static_cast<unsigned char*>(ws), stream, 0, pay_in);
+                                  static_cast<unsigned char*>(ws), stream, out32 ? 1 : 0, pay_in);
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 

@@ -30,7 +30,7 @@ namespace b2s {
 // defined with the local sort
 bool local_sort_pos32_supported(size_t n);
 int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
-                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream);
+                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, int out32 = 0);
 }  // namespace b2s
 #include "b2s_dist_host.h"
 #include "b2s_merge.cuh"
@@ -1231,6 +1231,137 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   return B2S_OK;
 }
 
+// ---- N-D tiles whose sort axis is the one split over the ranks ------------------------------
+// Every rank holds the same `rows` rows and a slice of each of them (extent_local elements,
+// slices in rank order).  All rows at once: the rows are dealt out to the ranks, each rank
+// receives the other ranks' slices of its rows (one exchange), sorts its now complete rows with
+// the segmented local sort, and sends every rank its slice of the sorted rows back (a second
+// exchange).  Exact extents come out by construction: no samples, no rebalancing step, and the
+// cost does not depend on the number of rows.  The reference runs its sample sort over all
+// segments and then shifts the results back into place (src/cupynumeric/sort/sort.cu:1351-1452,
+// 1759-1773, 799-1261).
+int b2s_dist_sort_nd_ops(int dtype, const void* tile_in, void* tile_out, int argsort, size_t rows, size_t extent_local,
+                         const b2s_comm_ops* ops, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                         void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
+{
+  int xf       = 0;
+  const int kb = kb_of(dtype, &xf);
+  if (kb == 0) return B2S_ERR_UNSUPPORTED;
+  if (alloc == nullptr || nranks < 1 || nranks > MAX_BUCKETS || rank < 0 || rank >= nranks) return B2S_ERR_INVALID_ARG;
+  if (nranks > 1 && (ops == nullptr || ops->all_gather == nullptr || ops->exchange == nullptr)) return B2S_ERR_INVALID_ARG;
+  if (rows * extent_local > 0 && (tile_in == nullptr || tile_out == nullptr)) return B2S_ERR_INVALID_ARG;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  Scratch mem{alloc, release, alloc_ctx, {}};
+  Status st;
+  const size_t out_elem = argsort ? 8 : (size_t)kb;
+
+  // ---- everybody's extent along the sort axis, and whether everybody is in one piece ----
+  std::vector<long long> all((size_t)4 * nranks);
+  long long mine[4] = {(long long)extent_local, (long long)rows, 0, 0};
+  long long* d_all  = static_cast<long long*>(mem.get(sizeof(long long) * 4 * (nranks + 1)));
+  if (d_all == nullptr) {
+    st.set(B2S_ERR_WORKSPACE);
+    d_all = reinterpret_cast<long long*>(emergency_area());
+    if (d_all == nullptr) return B2S_ERR_CUDA;
+  }
+  auto agree = [&]() -> int {
+    // all-gather of (extent, rows, status): returns the first failure any rank reported
+    mine[2] = st.code;
+    st.cuda(cudaMemcpyAsync(d_all + 4 * nranks, mine, sizeof(mine), cudaMemcpyHostToDevice, stream));
+    if (nranks > 1) {
+      if (barrier) barrier(barrier_ctx);
+      st.set(ops->all_gather(ops->ctx, d_all + 4 * nranks, d_all, sizeof(mine), stream));
+      if (barrier) barrier(barrier_ctx);
+    } else {
+      st.cuda(cudaMemcpyAsync(d_all, d_all + 4, sizeof(mine), cudaMemcpyDeviceToDevice, stream));
+    }
+    st.cuda(cudaMemcpyAsync(all.data(), d_all, sizeof(long long) * 4 * nranks, cudaMemcpyDeviceToHost, stream));
+    st.cuda(cudaStreamSynchronize(stream));
+    if (!st.ok()) return st.code;
+    for (int p = 0; p < nranks; ++p)
+      if (all[4 * p + 2] != B2S_OK) return (int)all[4 * p + 2];
+    return B2S_OK;
+  };
+  int rc = agree();
+  if (rc != B2S_OK) return rc;
+  std::vector<long long> lo(nranks + 1, 0);
+  for (int p = 0; p < nranks; ++p) {
+    if (all[4 * p + 1] != (long long)rows) return B2S_ERR_INVALID_ARG;  // the ranks disagree on the tile's shape
+    lo[p + 1] = lo[p] + all[4 * p];
+  }
+  const long long extent_global = lo[nranks];
+  if (rows == 0 || extent_global == 0) return B2S_OK;
+  auto row_lo = [&](int q) { return (long long)rows * q / nranks; };   // rank q sorts rows [row_lo(q), row_lo(q+1))
+  const long long my_rows = row_lo(rank + 1) - row_lo(rank);
+
+  // ---- buffers: what I receive (one block per source), my complete rows, their sorted form ----
+  const size_t full = (size_t)my_rows * (size_t)extent_global;
+  unsigned char* stage_in  = static_cast<unsigned char*>(mem.get(full * kb + 256));
+  unsigned char* full_rows = static_cast<unsigned char*>(mem.get(full * kb + 256));
+  unsigned char* sorted    = static_cast<unsigned char*>(mem.get(full * out_elem + 256));
+  unsigned char* stage_out = static_cast<unsigned char*>(mem.get(full * out_elem + 256));
+  size_t ws_bytes = 0;
+  void* sort_ws   = nullptr;
+  if (full > 0) {
+    st.set(b2s_workspace_bytes(dtype, full, (size_t)extent_global, argsort, &ws_bytes));
+    if (st.ok()) sort_ws = mem.get(ws_bytes);
+  }
+  if (!stage_in || !full_rows || !sorted || !stage_out || (full > 0 && sort_ws == nullptr)) st.set(B2S_ERR_WORKSPACE);
+  rc = agree();  // nobody enters the exchanges unless everybody can
+  if (rc != B2S_OK) return rc;
+
+  const unsigned char* in = static_cast<const unsigned char*>(tile_in);
+  unsigned char* out      = static_cast<unsigned char*>(tile_out);
+  std::vector<const void*> sp(nranks, nullptr);
+  std::vector<void*> rp(nranks, nullptr);
+  std::vector<size_t> sb(nranks, 0), rb(nranks, 0);
+  // ---- first exchange: rank q gets rows [row_lo(q), row_lo(q+1)) of my slice, a contiguous block ----
+  for (int q = 0; q < nranks; ++q) {
+    const long long nq = row_lo(q + 1) - row_lo(q);
+    sp[q] = in + (size_t)row_lo(q) * extent_local * kb;
+    sb[q] = (size_t)nq * extent_local * kb;
+    rp[q] = stage_in + (size_t)my_rows * (size_t)lo[q] * kb;   // blocks in source order
+    rb[q] = (size_t)my_rows * (size_t)all[4 * q] * kb;
+  }
+  if (sb[rank] > 0) st.cuda(cudaMemcpyAsync(rp[rank], sp[rank], sb[rank], cudaMemcpyDeviceToDevice, stream));
+  if (nranks > 1) {
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->exchange(ops->ctx, sp.data(), sb.data(), rp.data(), rb.data(), stream));
+    if (barrier) barrier(barrier_ctx);
+  }
+  // the block of source q holds columns [lo[q], lo[q+1]) of my rows
+  for (int q = 0; q < nranks && my_rows > 0; ++q) {
+    if (all[4 * q] == 0) continue;
+    st.cuda(cudaMemcpy2DAsync(full_rows + (size_t)lo[q] * kb, (size_t)extent_global * kb, rp[q], (size_t)all[4 * q] * kb,
+                              (size_t)all[4 * q] * kb, (size_t)my_rows, cudaMemcpyDeviceToDevice, stream));
+  }
+  // ---- my rows, complete: one segmented sort; argsort positions are positions in the whole row ----
+  if (full > 0 && st.ok())
+    st.set(b2s_local_sort(dtype, full_rows, argsort ? nullptr : sorted, argsort ? reinterpret_cast<int64_t*>(sorted) : nullptr, full,
+                          (size_t)extent_global, 0, 0, 1, sort_ws, ws_bytes, stream));
+  // ---- second exchange: every rank gets its columns of my sorted rows back ----
+  for (int q = 0; q < nranks; ++q) {
+    const long long nq = row_lo(q + 1) - row_lo(q);
+    unsigned char* block = stage_out + (size_t)my_rows * (size_t)lo[q] * out_elem;
+    if (my_rows > 0 && all[4 * q] > 0)
+      st.cuda(cudaMemcpy2DAsync(block, (size_t)all[4 * q] * out_elem, sorted + (size_t)lo[q] * out_elem, (size_t)extent_global * out_elem,
+                                (size_t)all[4 * q] * out_elem, (size_t)my_rows, cudaMemcpyDeviceToDevice, stream));
+    sp[q] = block;
+    sb[q] = (size_t)my_rows * (size_t)all[4 * q] * out_elem;
+    rp[q] = out + (size_t)row_lo(q) * extent_local * out_elem;   // rows sorted by rank q, my columns
+    rb[q] = (size_t)nq * extent_local * out_elem;
+  }
+  if (sb[rank] > 0) st.cuda(cudaMemcpyAsync(rp[rank], sp[rank], sb[rank], cudaMemcpyDeviceToDevice, stream));
+  if (nranks > 1) {
+    if (barrier) barrier(barrier_ctx);
+    st.set(ops->exchange(ops->ctx, sp.data(), sb.data(), rp.data(), rb.data(), stream));
+    if (barrier) barrier(barrier_ctx);
+  }
+  if (sort_ws != nullptr && st.ok() && dtype != B2S_COMPLEX128) st.set(b2s_check_status(sort_ws, stream));
+  else st.cuda(cudaStreamSynchronize(stream));
+  return st.code;
+}
+
 // The same two calls over an NCCL communicator.
 int b2s_dist_sort_1d(int dtype, const void* keys_in, size_t n_local, int64_t global_offset, int argsort,
                      void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
@@ -1276,6 +1407,24 @@ int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, 
   if (rc != B2S_OK) return rc;
   rc = b2s_dist_rebalance_1d_ops(elem_bytes, part, part_len, part_global_start, out, out_len, out_global_start, &ops, rank, nranks,
                                  alloc, release, alloc_ctx, barrier, barrier_ctx, cuda_stream);
+  b2s_nccl_comm_ops_release(&ops);
+  return rc;
+}
+
+int b2s_dist_sort_nd(int dtype, const void* tile_in, void* tile_out, int argsort, size_t rows, size_t extent_local,
+                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                     b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream)
+{
+  if (nranks <= 1)
+    return b2s_dist_sort_nd_ops(dtype, tile_in, tile_out, argsort, rows, extent_local, nullptr, rank, nranks, alloc, release,
+                                alloc_ctx, barrier, barrier_ctx, cuda_stream);
+  if (nccl_comm == nullptr) return B2S_ERR_INVALID_ARG;
+  int word = 0;  // the two exchanges need no barrier word
+  b2s_comm_ops ops{};
+  int rc = b2s_nccl_comm_ops(&ops, nccl_comm, rank, nranks, &word);
+  if (rc != B2S_OK) return rc;
+  rc = b2s_dist_sort_nd_ops(dtype, tile_in, tile_out, argsort, rows, extent_local, &ops, rank, nranks, alloc, release, alloc_ctx,
+                            barrier, barrier_ctx, cuda_stream);
   b2s_nccl_comm_ops_release(&ops);
   return rc;
 }

@@ -264,7 +264,11 @@ __device__ __forceinline__ void fixup_body(const FixDesc& f, unsigned int n, int
     }
   }
   if (f.synth_idx32 != nullptr) {
-    for (size_t i = gthread; i < n; i += gstride) f.synth_idx32[i] = (uint32_t)i;
+    if (f.widen_src != nullptr) {
+      for (size_t i = gthread; i < n; i += gstride) f.synth_idx32[i] = f.widen_src[i];
+    } else {
+      for (size_t i = gthread; i < n; i += gstride) f.synth_idx32[i] = (uint32_t)i;
+    }
   }
 }
 

@@ -209,6 +209,23 @@ int b2s_dist_rebalance_1d(size_t elem_bytes, const void* part, size_t part_len, 
                           int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
                           b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream);
 
+/* Sorts an N-D tile along its last axis when that axis is the one split over the ranks: every rank
+ * holds the same `rows` rows and `extent_local` consecutive elements of each (slices in rank order,
+ * dense row-major).  tile_out has the tile's shape and receives this rank's slice of every sorted
+ * row - values, or (argsort) int64 positions along the whole axis.  All rows go through at once:
+ * the rows are dealt out to the ranks, completed by one exchange, sorted by the segmented local
+ * sort and returned by a second exchange; exact extents, no rebalancing step.  Every rank calls.
+ * Worth it when there are at least as many rows as ranks; a few long rows are better served by
+ * b2s_dist_sort_1d + b2s_dist_rebalance_1d per row.  Synchronises the stream.
+ * Replaces sample_sort_nccl_nd + rebalance_data for this case
+ * (src/cupynumeric/sort/sort.cu:1270-1784, 799-1261). */
+int b2s_dist_sort_nd_ops(int dtype, const void* tile_in, void* tile_out, int argsort, size_t rows, size_t extent_local,
+                         const b2s_comm_ops* ops, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release,
+                         void* alloc_ctx, b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream);
+int b2s_dist_sort_nd(int dtype, const void* tile_in, void* tile_out, int argsort, size_t rows, size_t extent_local,
+                     void* nccl_comm, int rank, int nranks, b2s_alloc_fn alloc, b2s_free_fn release, void* alloc_ctx,
+                     b2s_barrier_fn barrier, void* barrier_ctx, void* cuda_stream);
+
 /* Stable merge of `nruns` (<= 32) sorted runs, ties taken from the lower-numbered run first:
  * out receives the merged keys, or - when run_idx is not NULL - only the merged int64 payloads.
  * `ws`: b2s_kway_merge_workspace_bytes(total, nruns) bytes of device scratch.  One pass over the
@@ -272,6 +289,29 @@ int b2s_searchsorted(int dtype, const void* sorted_tile, size_t n_tile, int64_t 
 int b2s_unique_workspace_bytes(size_t n, size_t* bytes);
 int b2s_unique_sorted(int dtype, const void* sorted, size_t n, void* out, size_t* out_len, void* ws,
                       size_t ws_bytes, void* cuda_stream);
+
+/* ---- PARTITION by selection, LEXSORT over several keys --------------------------------------- */
+
+/* Partitions a 1-D tile around its element of rank `kth` (0-based, in the sort's total order)
+ * without sorting it: keys_out (may be NULL) receives the elements below that key, then those equal
+ * to it, then those above; idx_out (may be NULL) the positions (index_offset + i) in the same
+ * arrangement.  The order inside the three blocks is unspecified, as numpy.partition allows.  A
+ * radix select over the key bytes finds the key (one pass per byte), one more pass writes the
+ * blocks.  keys_out must not be keys_in; n < 2^32.  `ws`: b2s_partition_workspace_bytes() bytes,
+ * 256-byte aligned.  The reference sorts instead (cupynumeric/_thunk/deferred.py:5476-5494). */
+int b2s_partition_workspace_bytes(size_t* bytes);
+int b2s_partition_1d(int dtype, const void* keys_in, void* keys_out, int64_t* idx_out, size_t n, size_t kth,
+                     int64_t index_offset, void* ws, size_t ws_bytes, void* cuda_stream);
+
+/* Indices that sort `nkeys` keys of the same shape lexicographically along the last axis, keys[0]
+ * being the least significant (numpy.lexsort's convention): `volume` elements per key in
+ * `volume / segment` rows; idx_out receives int64 positions inside each row.  One stable argsort per
+ * key with the order so far carried through it; no step leaves the library.  `ws`:
+ * b2s_lexsort_workspace_bytes(...) bytes, 256-byte aligned.  Replaces the chain of ARGSORT tasks
+ * and gathers of cupynumeric/_module/ssc_sorting.py:423-444. */
+int b2s_lexsort_workspace_bytes(int nkeys, const int* dtypes, size_t volume, size_t segment, size_t* bytes);
+int b2s_lexsort(int nkeys, const int* dtypes, const void* const* keys, int64_t* idx_out, size_t volume, size_t segment,
+                void* ws, size_t ws_bytes, void* cuda_stream);
 
 /* ---- measurement aids (no counterpart in the reference, which relies on Legate's profiler,
  * cupynumeric/_utils/profiling.py:33-73) ------------------------------------------------------ */

@@ -196,3 +196,66 @@ def test_a_rank_whose_allocator_fails_takes_everybody_out_together(cuda_device, 
         assert all(st != 0 for st in statuses), statuses
     for _, _, _, pool in res:
         assert len(pool.live) == 0, "scratch memory was not handed back"
+
+
+def run_ranks_nd(tiles, argsort, timeout=120):
+    """b2s_dist_sort_nd_ops with thread ranks: ``tiles[r]`` is rank r's (rows, extent_r) slice."""
+    lib = _lib.lib()
+    nranks = len(tiles)
+    ops = (_lib.CommOps * nranks)()
+    _lib.check(lib.b2s_thread_comm_create(nranks, ops), "b2s_thread_comm_create")
+    out, errors = [None] * nranks, []
+
+    def rank_main(r):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                tile = np.ascontiguousarray(tiles[r])
+                d_in = to_device(tile).reshape(tile.shape) if tile.size else None
+                d_out = torch.empty(tile.shape, dtype=torch.int64 if argsort else (d_in.dtype if d_in is not None else torch.int32),
+                                    device="cuda")
+                stream.synchronize()
+                pool = Pool()
+                st = lib.b2s_dist_sort_nd_ops(_lib.DTYPE_CODE[tile.dtype], d_in.data_ptr() if d_in is not None else None,
+                                              d_out.data_ptr() if tile.size else None, int(argsort), tile.shape[0], tile.shape[1],
+                                              ctypes.byref(ops[r]), r, nranks, ctypes.cast(pool.alloc_cb, ctypes.c_void_p),
+                                              ctypes.cast(pool.free_cb, ctypes.c_void_p), None, None, None, stream.cuda_stream)
+                res = d_out.cpu().numpy() if argsort else d_out.cpu().numpy().view(tile.dtype)
+                out[r] = (st, res, pool)
+        except Exception as e:  # pragma: no cover
+            errors.append((r, repr(e)))
+
+    threads = [threading.Thread(target=rank_main, args=(r,), daemon=True) for r in range(nranks)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout)
+    assert not [t for t in threads if t.is_alive()], "a rank is still waiting for the others"
+    assert not errors, errors
+    for r in range(nranks):
+        lib.b2s_thread_comm_destroy(ctypes.byref(ops[r]))
+    return out
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.float64, np.int16, np.complex64])
+@pytest.mark.parametrize("shape", [(8, (100, 37, 250)), (300, (7, 0, 5, 9)), (5, (3000, 9000)), (2, (10, 10, 10)), (64, (4096, 4096))])
+def test_split_axis_rows_all_at_once(cuda_device, dtype, shape):
+    """Rows whose sort axis is split over the ranks (ragged extents, an empty slice, fewer rows than
+    ranks, rows too long for the on-chip sort): every rank ends up with its own extent of every
+    sorted row, values and stable argsort positions."""
+    rows, extents = shape
+    rng = np.random.default_rng(rows + len(extents))
+    if np.dtype(dtype).kind == "c":
+        whole = (rng.integers(-9, 9, (rows, sum(extents))) + 1j * rng.integers(-9, 9, (rows, sum(extents)))).astype(dtype)
+    else:
+        whole = rng.integers(-50, 50, (rows, sum(extents))).astype(dtype)
+    cuts = np.cumsum((0,) + tuple(extents))
+    tiles = [whole[:, cuts[r]:cuts[r + 1]] for r in range(len(extents))]
+    for argsort in (False, True):
+        res = run_ranks_nd(tiles, argsort)
+        assert all(st == 0 for st, _, _ in res), [st for st, _, _ in res]
+        got = np.concatenate([r for _, r, _ in res], axis=1)
+        want = np.argsort(whole, axis=1, kind="stable") if argsort else np.sort(whole, axis=1, kind="stable")
+        assert np.array_equal(got, want)
+        assert all(len(pool.live) == 0 for _, _, pool in res)
