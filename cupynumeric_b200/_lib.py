@@ -97,6 +97,7 @@ SIGNATURES = {
     "b2s_workspace_bytes": (_I, [_I, _SZ, _SZ, _I, ctypes.POINTER(_SZ)]),
     "b2s_local_sort": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _I, _I, _P, _SZ, _P]),
     "b2s_check_status": (_I, [_P, _P]),
+    "b2s_selftest_wait_timeout": (_I, [_P, _SZ, _P]),
     "b2s_local_sort_noalloc": (_I, [_I, _P, _P, _P, _SZ, _SZ, _I64, _I, _P]),
     "b2s_noalloc_check_status": (_I, [_P]),
     "b2s_dist_sort_1d": (_I, [_I, _P, _SZ, _I64, _I, _P, _I, _I, _P, _P, _P, _P, _P,

@@ -301,6 +301,51 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 
+// Self-test of the bounded waits.  Sorts a small array of its own whose first tile is never
+// processed (the tile tickets of the first pass start at 1), with a poll limit of a few thousand:
+// every later tile waits for the first tile's look-back entry, gives up within milliseconds,
+// records DEV_ERR_TIMEOUT and raises the abort flag; the remaining passes see the flag and
+// return.  Nothing traps, faults or waits without a bound; the workspace and the context stay usable.
+namespace b2s {
+__global__ void selftest_fill_kernel(uint32_t* keys, unsigned int n)
+{
+  for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) keys[i] = i * 2654435761u;
+}
+}  // namespace b2s
+
+int b2s_selftest_wait_timeout(void* ws, size_t ws_bytes, void* cuda_stream)
+{
+  constexpr unsigned int N = 1u << 16;  // a dozen tiles
+  const auto lay           = radix_1d_layout<4>(N, false);
+  const size_t need        = lay.total + 2 * (size_t)N * 4;
+  if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  unsigned char* base = static_cast<unsigned char*>(ws);
+  Ctrl* ctrl          = reinterpret_cast<Ctrl*>(base);
+  uint32_t* in        = reinterpret_cast<uint32_t*>(base + lay.total);
+  uint32_t* out       = in + N;
+  unsigned int* lb    = reinterpret_cast<unsigned int*>(base + lay.off_lookback);
+  if (cudaMemsetAsync(base, 0, lay.off_keys[0], stream) != cudaSuccess) return B2S_ERR_CUDA;
+  selftest_fill_kernel<<<64, 256, 0, stream>>>(in, N);
+  RouteArgs ra{};
+  ra.keys_in     = in;
+  ra.keys_out    = out;
+  ra.tmp_keys[0] = base + lay.off_keys[0];
+  ra.tmp_keys[1] = base + lay.off_keys[1];
+  ra.n           = N;
+  ra.npass       = 4;
+  ra.key_bytes   = 4;
+  hist_kernel<4, XF_UNSIGNED><<<16, HIST_THREADS, 0, stream>>>(in, N, ctrl, ra);
+  // the sabotage: the first pass hands out tickets 1, 2, ... so that tile 0 is never taken, and a
+  // short poll limit
+  const unsigned int one = 1, limit = 4096;
+  if (cudaMemcpyAsync(&ctrl->tile_counter[0], &one, 4, cudaMemcpyHostToDevice, stream) != cudaSuccess) return B2S_ERR_CUDA;
+  if (cudaMemcpyAsync(&ctrl->spin_limit, &limit, 4, cudaMemcpyHostToDevice, stream) != cudaSuccess) return B2S_ERR_CUDA;
+  const SegGeom geo{N, lay.tiles, 1u, 4, nullptr};
+  const cudaError_t e = launch_sweeps<4, XF_UNSIGNED, false>(ctrl, lb, lay.tiles, geo, 0, stream);
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
+}
+
 int b2s_check_status(void* ws, void* cuda_stream)
 {
   if (ws == nullptr) return B2S_ERR_INVALID_ARG;

@@ -136,7 +136,8 @@ struct Ctrl {
   unsigned int abort;                   // set with status; every later wait gives up at once
   unsigned int tile_counter[MAX_PASSES];
   unsigned int hist_done;               // CTAs of the histogram kernel that have added their counts
-  unsigned int pad_[5];
+  unsigned int spin_limit;              // 0: SPIN_LIMIT; else the poll limit of the look-back wait (self-test)
+  unsigned int pad_[4];
   unsigned int hist[MAX_PASSES][RADIX]; // digit counts, then (after the scan kernel) exclusive bases
   PassDesc pass[MAX_PASSES];
   FixDesc fix;

@@ -564,7 +564,7 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
       // window are independent, so a run of tiles that have only published their counts costs
       // one memory latency per window instead of one per tile.
       int t              = (int)tile - 1;
-      unsigned int spins = 0;
+      unsigned int spins = 0, spin_cap = SPIN_LIMIT;
       bool gave_up       = false;
       bool done          = false;
       while (!done) {
@@ -588,7 +588,8 @@ onesweep_kernel(Ctrl* ctrl, unsigned int* __restrict__ lookback, int pass, SegGe
         }
         t -= used;
         if (!done && used == 0) {
-          if (++spins > SPIN_LIMIT || ((spins & 1023u) == 0 && ld_relaxed(&ctrl->abort))) {
+          if (spins == 0 && ctrl->spin_limit != 0) spin_cap = ctrl->spin_limit;
+          if (++spins > spin_cap || ((spins & 1023u) == 0 && ld_relaxed(&ctrl->abort))) {
             gave_up = true;
             break;
           }

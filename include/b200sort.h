@@ -97,6 +97,14 @@ int b2s_local_sort(int dtype, const void* keys_in, void* keys_out, int64_t* idx_
  * CUPYNUMERIC_CHECK_CUDA_STREAM (src/cupynumeric/cuda_help.h:291-302). */
 int b2s_check_status(void* ws, void* cuda_stream);
 
+/* Self-test of the bounded device-side waits: runs a small sort of the library's own whose first
+ * tile is deliberately never processed, with a poll limit of a few thousand, so that the waits on
+ * that tile run out within milliseconds.  Afterwards b2s_check_status(ws, stream) must answer
+ * B2S_ERR_TIMEOUT, and the workspace, the stream and the context must still be usable.  Nothing
+ * traps, faults or waits without a bound.  `ws`: at least 2 MiB, 256-byte aligned.  (The reference
+ * has no bounded waits to test: its library kernels are not its own.) */
+int b2s_selftest_wait_timeout(void* ws, size_t ws_bytes, void* cuda_stream);
+
 /* Same contract as b2s_local_sort, for callers that cannot hand over a workspace because they
  * cannot allocate one: for instance a task body under a runtime that forbids cudaMalloc while
  * tasks are in flight, or a thread whose memory pool is exhausted.  It has no counterpart in the

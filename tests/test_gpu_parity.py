@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from oracle import complex_lex_argsort, np_argsort, np_sort, np_task_sort, thrust_task_sort
-from tests.helpers import ALL_DTYPES, assert_bit_equal, cabi_local_sort, random_keys
+from tests.helpers import ALL_DTYPES, assert_bit_equal, cabi_local_sort, random_keys, to_device, to_host
 
 pytestmark = pytest.mark.gpu
 
@@ -245,3 +245,29 @@ def test_config_shapes_reduced(cuda_device):
     a = w.c5_uint64_nearly_sorted_shard(1 << 20)
     _, got = cabi_local_sort(a, a.size, True)
     assert np.array_equal(got, np.argsort(a, kind="stable"))
+
+
+def test_bounded_wait_runs_out_and_is_reported(cuda_device):
+    """A look-back wait that can never be satisfied (the library's own self-test: the first tile of
+    a small sort is never processed) ends after a few thousand polls: the kernels return, the
+    status word reads B2S_ERR_TIMEOUT, and the same workspace then serves a correct sort."""
+    import ctypes
+
+    import torch
+
+    from cupynumeric_b200 import _lib
+
+    lib = _lib.lib()
+    ws = torch.empty(8 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.b2s_selftest_wait_timeout(ws.data_ptr(), ws.numel(), stream) == 0
+    assert lib.b2s_check_status(ws.data_ptr(), stream) == 5          # B2S_ERR_TIMEOUT
+    a = np.random.default_rng(0).integers(0, 1 << 31, 100_000).astype(np.uint32)
+    d_in, d_out = to_device(a), torch.empty(a.size, dtype=torch.int32, device="cuda")
+    need = ctypes.c_size_t()
+    _lib.check(lib.b2s_workspace_bytes(_lib.DTYPE_CODE[a.dtype], a.size, a.size, 0, ctypes.byref(need)), "ws")
+    assert need.value <= ws.numel()
+    _lib.check(lib.b2s_local_sort(_lib.DTYPE_CODE[a.dtype], d_in.data_ptr(), d_out.data_ptr(), None, a.size, a.size, 0, 1, 1,
+                                  ws.data_ptr(), ws.numel(), stream), "b2s_local_sort")
+    assert lib.b2s_check_status(ws.data_ptr(), stream) == 0
+    assert np.array_equal(to_host(d_out, a.dtype), np.sort(a))
