@@ -163,9 +163,20 @@ def rows_worker(rank: int, world: int, port: int, ret):
             whole = np.concatenate([p for _, p in sorted(parts, key=lambda t: t[0])])
             out.copy_(torch.from_numpy(whole[out_start:out_start + out.numel()].copy()))
 
+        def fake_dist_sort_nd(tile, argsort):
+            """Same contract as dist_sort_nd: every rank holds a slice of every row; returns this
+            rank's slice of every sorted row (values, or positions along the whole row)."""
+            tiles = [None] * world
+            dist.all_gather_object(tiles, tile.numpy().copy())
+            full = np.concatenate(tiles, axis=1)
+            res = np.argsort(full, axis=1, kind="stable").astype(np.int64) if argsort else np.sort(full, axis=1, kind="stable")
+            lo = sum(t.shape[1] for t in tiles[:rank])
+            return torch.from_numpy(res[:, lo:lo + tile.shape[1]].copy())
+
         sort_mod.local_sort_tile = fake_local
         dist_mod.dist_sort_1d = fake_dist_sort
         dist_mod.rebalance_1d = fake_rebalance
+        dist_mod.dist_sort_nd = fake_dist_sort_nd
         assert runtime.num_procs == world
         whole = np.random.default_rng(9).integers(-50, 50, (8, 13)).astype(np.int32)
         block = whole[rank * 4:(rank + 1) * 4]
@@ -179,6 +190,14 @@ def rows_worker(rank: int, world: int, port: int, ret):
             want = (np.argsort(whole, axis=0, kind="stable") if argsort else np.sort(whole, axis=0, kind="stable"))
             ok_split &= bool(np.array_equal(res.base.numpy(), want[rank * 4:(rank + 1) * 4]))
             ok_split &= res.global_lo == rank * 4 and res.tiled_axis == 0
+        # fewer columns than ranks: each column takes the distributed 1-D sort and the move back
+        thin = whole[:, :1]
+        for argsort in (False, True):
+            res = create_deferred_thunk((4, 1), np.int64 if argsort else np.int32)
+            res.sort(DeferredArray(torch.from_numpy(thin[rank * 4:(rank + 1) * 4].copy()), global_lo=rank * 4), argsort=argsort,
+                     axis=0, kind="stable")
+            want = (np.argsort(thin, axis=0, kind="stable") if argsort else np.sort(thin, axis=0, kind="stable"))
+            ok_split &= bool(np.array_equal(res.base.numpy(), want[rank * 4:(rank + 1) * 4]))
         ret.put((rank, ok_rows, ok_split))
     finally:
         dist.destroy_process_group()
