@@ -1171,11 +1171,11 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
       }
       if (sb[rank] > 0)  // my own piece stays on this GPU
         st.cuda(cudaMemcpyAsync(rp[rank], sp[rank], sb[rank], cudaMemcpyDeviceToDevice, stream));
-      prof::begin(prof::K_XCHG, stream);
+      const int rec = prof::begin(prof::K_XCHG, stream);
       if (barrier) barrier(barrier_ctx);
       st.set(ops->exchange(ops->ctx, sp.data(), sb.data(), rp.data(), rb.data(), stream));
       if (barrier) barrier(barrier_ctx);
-      prof::end(prof::K_XCHG, stream);
+      prof::end(rec, stream);
     }
   }
   trace.mark("partition", stream);

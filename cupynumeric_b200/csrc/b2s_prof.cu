@@ -1,6 +1,8 @@
 // Launch counters and optional per-kernel event timing (see include/b200sort.h:
-// b2s_profile_enable / b2s_profile_read / b2s_launch_count).  Process-wide and not
-// thread-safe by design: it is a measurement aid for single-threaded harnesses.
+// b2s_profile_enable / b2s_profile_read / b2s_launch_count).  Process-wide; launches may be
+// recorded from several host threads at once (ranks that are threads of one process).
+#include <atomic>
+#include <mutex>
 #include <vector>
 
 #include "../../include/b200sort.h"
@@ -13,10 +15,11 @@ struct Rec {
   int kind;
   cudaEvent_t a, b;
 };
-static bool g_enabled = false;
+static std::atomic<bool> g_enabled{false};
+static std::mutex g_mu;                   // guards the two vectors
 static std::vector<Rec> g_recs;           // event pairs in use since the last enable/reset
 static std::vector<cudaEvent_t> g_pool;   // spare events
-static unsigned long long g_launches[K_COUNT] = {};
+static std::atomic<unsigned long long> g_launches[K_COUNT];
 
 static cudaEvent_t take_event()
 {
@@ -30,20 +33,22 @@ static cudaEvent_t take_event()
   return e;
 }
 
-void begin(int kind, cudaStream_t stream)
+int begin(int kind, cudaStream_t stream)
 {
   ++g_launches[kind];
-  if (!g_enabled) return;
+  if (!g_enabled.load()) return -1;
+  std::lock_guard<std::mutex> lock(g_mu);
   Rec r{kind, take_event(), take_event()};
   cudaEventRecord(r.a, stream);
   g_recs.push_back(r);
+  return (int)g_recs.size() - 1;
 }
 
-void end(int kind, cudaStream_t stream)
+void end(int id, cudaStream_t stream)
 {
-  (void)kind;
-  if (!g_enabled || g_recs.empty()) return;
-  cudaEventRecord(g_recs.back().b, stream);
+  if (id < 0) return;
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (id < (int)g_recs.size()) cudaEventRecord(g_recs[id].b, stream);
 }
 
 static void recycle()
@@ -64,6 +69,8 @@ extern "C" {
 
 int b2s_profile_enable(int on)
 {
+  std::lock_guard<std::mutex> lock(g_mu);
+  g_enabled.store(false);
   recycle();
   // events are created here, not between the kernels that are being timed
   constexpr size_t RESERVE = 4096;
@@ -72,7 +79,7 @@ int b2s_profile_enable(int on)
     if (cudaEventCreate(&e) != cudaSuccess) break;
     g_pool.push_back(e);
   }
-  g_enabled = on != 0;
+  g_enabled.store(on != 0);
   return B2S_OK;
 }
 
@@ -81,6 +88,7 @@ int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches)
   if (kind < 0 || kind >= K_COUNT) return B2S_ERR_INVALID_ARG;
   double tot = 0;
   unsigned long long cnt = 0;
+  std::lock_guard<std::mutex> lock(g_mu);
   for (auto& r : g_recs) {
     if (r.kind != kind) continue;
     if (cudaEventSynchronize(r.b) != cudaSuccess) return B2S_ERR_CUDA;
@@ -96,10 +104,9 @@ int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches)
 
 unsigned long long b2s_launch_count(int kind)
 {
-  if (kind >= 0 && kind < K_COUNT) return g_launches[kind];
+  if (kind >= 0 && kind < K_COUNT) return g_launches[kind].load();
   unsigned long long t = 0;
-  for (int k = 0; k < K_COUNT; ++k)
-    if (k != K_XCHG) t += g_launches[k];  // the exchange is NCCL's work, not a kernel of this library
+  for (int k = 0; k < K_COUNT; ++k) t += g_launches[k].load();
   return t;
 }
 }

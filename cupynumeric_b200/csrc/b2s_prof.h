@@ -15,18 +15,19 @@ enum Kind : int {
   K_UNIT,         // segments of one element
   K_DIST,         // sample / splitter / cut kernels of the distributed sort
   K_MERGE,        // k-way merge
-  K_XCHG,         // the grouped NCCL send/recv exchange (not a kernel of this library)
+  K_XCHG,         // the partition kernel that writes into the destinations' buffers (or the collective exchange)
   K_COUNT
 };
 
-void begin(int kind, cudaStream_t stream);
-void end(int kind, cudaStream_t stream);
+// begin returns the record to hand to end (-1 when timing is off)
+int begin(int kind, cudaStream_t stream);
+void end(int id, cudaStream_t stream);
 
 struct Scope {
-  int kind;
+  int id;
   cudaStream_t stream;
-  Scope(int k, cudaStream_t s) : kind(k), stream(s) { begin(kind, stream); }
-  ~Scope() { end(kind, stream); }
+  Scope(int kind, cudaStream_t s) : id(begin(kind, s)), stream(s) {}
+  ~Scope() { end(id, stream); }
 };
 
 }  // namespace prof

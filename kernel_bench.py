@@ -6,6 +6,11 @@
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
         kernel_bench.py dist --dtype float32 --log2 27 [--argsort]
 
+    python kernel_bench.py dist-threads --ranks 8 --dtype float32 --log2 24 [--argsort]
+
+`dist-threads` runs the distributed sort with its ranks as threads of this process on ONE GPU (the
+thread form of the collectives): the partition kernels write into buffers of the same GPU, so this
+shows their cost without NVLink, and it is a single process that a profiler can follow.
 `merge` times b2s_kway_merge on `runs` sorted runs holding 2^log2 elements in all; `sort` times
 b2s_local_sort; `dist` (one process per GPU) times the distributed 1-D sort of 2^log2 keys per GPU,
 first without the per-kernel events (the step time), then with them (where the time goes).
@@ -149,6 +154,67 @@ def bench_dist(args) -> None:
     dist.destroy_process_group()
 
 
+def bench_dist_threads(args) -> None:
+    import threading
+
+    lib = _lib.lib()
+    nranks, n = args.ranks, 1 << args.log2
+    dtype = getattr(torch, args.dtype)
+    code = _lib.DTYPE_CODE[np.dtype(args.dtype)]
+    torch.manual_seed(1)
+    shards = [_random(dtype, n) for _ in range(nranks)]
+    torch.cuda.synchronize()
+
+    class Pool:
+        def __init__(self):
+            self.live = {}
+            self.alloc_cb = _lib.ALLOC_FN(self._alloc)
+            self.free_cb = _lib.FREE_FN(self._free)
+
+        def _alloc(self, _ctx, nbytes):
+            t = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device="cuda")
+            self.live[t.data_ptr()] = t
+            return t.data_ptr()
+
+        def _free(self, _ctx, ptr):
+            self.live.pop(ptr, None)
+
+    def one_call():
+        ops = (_lib.CommOps * nranks)()
+        _lib.check(lib.b2s_thread_comm_create(nranks, ops), "b2s_thread_comm_create")
+        status = [None] * nranks
+
+        def rank_main(r):
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                pool = Pool()
+                out_ptr, out_len, out_start = ctypes.c_void_p(), ctypes.c_size_t(), ctypes.c_int64()
+                status[r] = lib.b2s_dist_sort_1d_ops(
+                    code, shards[r].data_ptr(), n, r * n, int(args.argsort), ctypes.byref(ops[r]), r, nranks,
+                    ctypes.cast(pool.alloc_cb, ctypes.c_void_p), ctypes.cast(pool.free_cb, ctypes.c_void_p), None, None, None,
+                    ctypes.byref(out_ptr), ctypes.byref(out_len), ctypes.byref(out_start), stream.cuda_stream)
+
+        threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(nranks)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        for r in range(nranks):
+            lib.b2s_thread_comm_destroy(ctypes.byref(ops[r]))
+        assert all(s == 0 for s in status), status
+
+    for _ in range(args.warmup):
+        one_call()
+    lib.b2s_profile_enable(1)
+    for _ in range(args.iters):
+        one_call()
+    torch.cuda.synchronize()
+    print(f"dist-threads {args.dtype} 2^{args.log2} x{nranks} ranks on one GPU argsort={args.argsort}; all ranks' kernels per call: "
+          f"{_report(lib, args.iters)}")
+    lib.b2s_profile_enable(0)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -166,7 +232,12 @@ def main() -> None:
     d.add_argument("--dtype", default="float32")
     d.add_argument("--log2", type=int, default=27)
     d.add_argument("--argsort", action="store_true")
-    for p in (m, s, d):
+    t = sub.add_parser("dist-threads")
+    t.add_argument("--ranks", type=int, default=8)
+    t.add_argument("--dtype", default="float32")
+    t.add_argument("--log2", type=int, default=24)
+    t.add_argument("--argsort", action="store_true")
+    for p in (m, s, d, t):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
@@ -177,7 +248,7 @@ def main() -> None:
         bench_dist(args)
         return
     torch.cuda.set_device(0)
-    (bench_merge if args.what == "merge" else bench_sort)(args)
+    {"merge": bench_merge, "sort": bench_sort, "dist-threads": bench_dist_threads}[args.what](args)
 
 
 if __name__ == "__main__":
