@@ -44,13 +44,13 @@ inline size_t radix_ws(int kb, size_t n, bool pairs)
 
 inline cudaError_t radix_any(int kb, int xf, const void* in, void* out, int64_t* idx, unsigned int n,
                              int64_t off, unsigned char* ws, cudaStream_t s, int idx32 = 0,
-                             const uint32_t* idx_in = nullptr)
+                             const uint32_t* idx_in = nullptr, const unsigned int* hp = nullptr, int hn = 0)
 {
   switch (kb) {
-    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
-    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
-    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
-    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s, idx32, idx_in);
+    case 1: return launch_radix_1d<1>(xf, in, out, idx, n, off, ws, s, idx32, idx_in, hp, hn);
+    case 2: return launch_radix_1d<2>(xf, in, out, idx, n, off, ws, s, idx32, idx_in, hp, hn);
+    case 4: return launch_radix_1d<4>(xf, in, out, idx, n, off, ws, s, idx32, idx_in, hp, hn);
+    default: return launch_radix_1d<8>(xf, in, out, idx, n, off, ws, s, idx32, idx_in, hp, hn);
   }
 }
 
@@ -165,6 +165,25 @@ int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in,
   if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
   const cudaError_t e = radix_any(di.kb, di.xf, keys_in, nullptr, idx_out, (unsigned int)n, index_offset,
                                   static_cast<unsigned char*>(ws), stream, out32 ? 1 : 0, pay_in);
+  return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
+}
+
+// Stable 1-D sort of what a rank of the distributed sort received: keys only (keys_out) or an
+// argsort with the 32-bit payloads carried through the passes (pay_in, idx_out).  The digit
+// histograms of the keys come ready-made in `nparts` pieces, counted by the senders.
+int local_sort_received(int dtype, const void* keys_in, void* keys_out, const uint32_t* pay_in, int64_t* idx_out, size_t n,
+                        int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, const unsigned int* hist_parts,
+                        int nparts)
+{
+  DtypeInfo di;
+  if (!dtype_info(dtype, &di) || !local_sort_pos32_supported(n)) return B2S_ERR_UNSUPPORTED;
+  if (keys_in == nullptr || (keys_out == nullptr) == (idx_out == nullptr)) return B2S_ERR_INVALID_ARG;
+  size_t need = 0;
+  int rc      = b2s_workspace_bytes(dtype, n, n, idx_out != nullptr, &need);
+  if (rc != B2S_OK) return rc;
+  if (ws == nullptr || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return B2S_ERR_WORKSPACE;
+  const cudaError_t e = radix_any(di.kb, di.xf, keys_in, keys_out, idx_out, (unsigned int)n, index_offset,
+                                  static_cast<unsigned char*>(ws), stream, 0, pay_in, hist_parts, nparts);
   return e == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
 }
 

@@ -31,6 +31,9 @@ namespace b2s {
 bool local_sort_pos32_supported(size_t n);
 int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
                          int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, int out32 = 0);
+int local_sort_received(int dtype, const void* keys_in, void* keys_out, const uint32_t* pay_in, int64_t* idx_out, size_t n,
+                        int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, const unsigned int* hist_parts,
+                        int nparts);
 }  // namespace b2s
 #include "b2s_dist_host.h"
 #include "b2s_merge.cuh"
@@ -841,7 +844,8 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   const size_t o_totals = take(8 * MAX_BUCKETS), o_mineB = take(sizeof(BlockB)), o_allB = take(sizeof(BlockB) * nranks);
   const long long nchunks = (ntiles + FP_CHUNK_TILES - 1) / FP_CHUNK_TILES;
   // zeroed together: the partition kernels' status word and the per-chunk sums of the tile counts
-  const size_t zero_bytes = 256 + 8 * (size_t)FP_NB * (size_t)(nchunks > 0 ? nchunks : 1);
+  constexpr size_t SENT_BYTES = (size_t)FP_NB * 8 * RADIX * 4;
+  const size_t zero_bytes = 256 + SENT_BYTES + 8 * (size_t)FP_NB * (size_t)(nchunks > 0 ? nchunks : 1);
   const size_t o_zero     = take(zero_bytes);
   size_t sample_ws_bytes = 0;
   b2s_workspace_bytes(B2S_UINT64, (size_t)S_all, (size_t)S_all, 1, &sample_ws_bytes);
@@ -853,8 +857,11 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     ctl = emergency_area();
     if (ctl == nullptr) return B2S_ERR_CUDA;  // not even the library's own device memory answers
   }
-  // receive buffers the other ranks write into
-  void* recv_keys = have_ctl ? mem.get((size_t)capacity * kb + 256) : nullptr;
+  // receive buffers the other ranks write into; in front of the keys a landing area for the digit
+  // histograms of what every rank sends here (one [8][256] table of counts per source rank)
+  constexpr size_t LANDING_BYTES = (size_t)MAX_BUCKETS * 8 * RADIX * 4;
+  unsigned char* recv_block = have_ctl ? static_cast<unsigned char*>(mem.get(LANDING_BYTES + (size_t)capacity * kb + 256)) : nullptr;
+  void* recv_keys = recv_block ? recv_block + LANDING_BYTES : nullptr;
   void* recv_pay  = (have_ctl && argsort) ? mem.get((size_t)capacity * pay_cap_bytes + 256) : nullptr;
   if (have_ctl && (recv_keys == nullptr || (argsort && recv_pay == nullptr))) st.set(B2S_ERR_WORKSPACE);
 
@@ -865,7 +872,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   h_mineA.global_offset = global_offset;
   h_mineA.capacity      = capacity;
   {
-    void* bufs[PEER_BUFFERS] = {recv_keys, recv_pay};
+    void* bufs[PEER_BUFFERS] = {recv_block, recv_pay};
     export_buffers(bufs, argsort ? 2 : 1, &h_mineA.rec);
     if (!st.ok()) h_mineA.rec.ok = 0;
   }
@@ -901,7 +908,8 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   unsigned long long* d_toff = reinterpret_cast<unsigned long long*>(ctl + o_toff);
   long long* d_totals    = reinterpret_cast<long long*>(ctl + o_totals);
   unsigned int* d_status = reinterpret_cast<unsigned int*>(ctl + (have_ctl ? o_zero : 0));
-  unsigned long long* d_chunks = reinterpret_cast<unsigned long long*>(ctl + o_zero + 256);
+  unsigned long long* d_chunks = reinterpret_cast<unsigned long long*>(ctl + o_zero + 256 + SENT_BYTES);
+  unsigned int* d_sent         = reinterpret_cast<unsigned int*>(ctl + o_zero + 256);  // [FP_NB][kb][256] digit counts per destination
   if (have_ctl) st.cuda(cudaMemsetAsync(ctl + o_zero, 0, zero_bytes, stream));
   if (have_ctl && st.ok()) {
     unsigned long long* khi = reinterpret_cast<unsigned long long*>(ctl + o_khi);
@@ -980,7 +988,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     const PeerRecord& r = h_allA_hdr[p].rec;
     if (!r.ok || r.nbuf != (unsigned long long)(argsort ? 2 : 1)) { mapped = 0; break; }
     if (p == rank) {
-      peer_keys[p] = static_cast<unsigned char*>(recv_keys);
+      peer_keys[p] = recv_block;
       peer_pay[p]  = static_cast<unsigned char*>(recv_pay);
     } else if (r.pid == my_pid) {
       if (!same_process_reachable((int)r.device)) { mapped = 0; break; }
@@ -994,6 +1002,10 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
       peer_pay[p]  = argsort ? pbase + r.off[1] : nullptr;
     }
   }
+  // peer_keys[p] is rank p's receive block: landing area first, keys behind it
+  std::vector<unsigned char*> peer_landing = peer_keys;
+  for (int p = 0; p < nranks; ++p)
+    if (peer_keys[p] != nullptr) peer_keys[p] += LANDING_BYTES;
   trace.mark("map", stream);
 
   // ---- second all-gather: counts per destination, mapping flag, status ----
@@ -1107,6 +1119,11 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     for (int p = 0; p < nranks; ++p)
       if (flags[p * (sizeof(BlockB) / 8)] != B2S_OK) return (int)flags[p * (sizeof(BlockB) / 8)];
   }
+  // Direct writes with the register-counting kernels: the senders also count the digits of what
+  // they send, per destination, and hand every destination its table; the receiver's local sort
+  // then starts without reading its keys for a histogram.  (B2S_DIST_SENDER_HIST=0: off.)
+  const char* sh_env     = std::getenv("B2S_DIST_SENDER_HIST");
+  const bool sender_hist = direct && fast && !(sh_env != nullptr && sh_env[0] == '0');
   if (n > 0 && fast) {
     prof::Scope ps(prof::K_XCHG, stream);
     FpDst fd{};
@@ -1117,18 +1134,41 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     by_width(kb, [&](auto w) {
       constexpr int KB = decltype(w)::value;
       using Raw        = typename FpKey<KB>::Raw;
-      auto launch = [&](auto kern, size_t bytes) {
+      auto launch = [&](auto kern, size_t bytes, bool one_wave) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) return e;
-        kern<<<(unsigned int)ntiles, FP_THREADS, bytes, stream>>>(static_cast<const Raw*>(keys_in), n, xf, d_local, d_toff, fd,
-                                                                    (long long)global_offset, gmin, d_status);
+        long long grid = ntiles;
+        if (one_wave) {
+          int dev = 0, sms = 148, per_sm = 1;
+          cudaGetDevice(&dev);
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FP_THREADS, bytes);
+          grid = std::min<long long>(ntiles, (long long)sms * (per_sm < 1 ? 1 : per_sm));
+        }
+        kern<<<(unsigned int)grid, FP_THREADS, bytes, stream>>>(static_cast<const Raw*>(keys_in), n, xf, d_local, d_toff, fd,
+                                                                  (long long)global_offset, gmin, d_status, d_sent);
         return cudaGetLastError();
       };
-      if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0>, FpSmem<KB, 0>::BYTES);
-      if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4>, FpSmem<KB, 4>::BYTES);
-      return launch(part_scatter_fast_kernel<KB, 8>, FpSmem<KB, 8>::BYTES);
+      if (sender_hist) {
+        if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0, true>, FpSmem<KB, 0, true>::BYTES, true);
+        if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4, true>, FpSmem<KB, 4, true>::BYTES, true);
+        return launch(part_scatter_fast_kernel<KB, 8, true>, FpSmem<KB, 8, true>::BYTES, true);
+      }
+      if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0, false>, FpSmem<KB, 0, false>::BYTES, false);
+      if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4, false>, FpSmem<KB, 4, false>::BYTES, false);
+      return launch(part_scatter_fast_kernel<KB, 8, false>, FpSmem<KB, 8, false>::BYTES, false);
     });
     st.cuda(cudaGetLastError());
+  }
+  if (sender_hist) {
+    // also from a rank with an empty tile: its (all-zero) table is what the others expect
+    prof::Scope ps(prof::K_DIST, stream);
+    FpDst land{};
+    for (int d = 0; d < nranks; ++d) land.keys[d] = peer_landing[d];
+    hist_deliver_kernel<<<nranks, 256, 0, stream>>>(d_sent, land, kb, rank);
+    st.cuda(cudaGetLastError());
+  }
+  if (n > 0 && fast) {
   } else if (n > 0) {
     prof::Scope ps(prof::K_XCHG, stream);
     by_width16(kb, [&](auto w) {
@@ -1190,7 +1230,13 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     sort_ws = st.ok() ? mem.get(ws_bytes) : nullptr;
     if (st.ok() && sort_ws == nullptr) st.set(B2S_ERR_WORKSPACE);
     if (st.ok()) {
-      if (!argsort) {
+      const bool parts_ok = sender_hist && local_sort_pos32_supported((size_t)n_recv) && (size_t)n_recv < single_limit();
+      if (parts_ok && (!argsort || payb == 4)) {
+        // the senders counted the digits: no histogram pass over the received keys
+        st.set(local_sort_received(dtype, recv_keys, argsort ? nullptr : result, argsort ? static_cast<const uint32_t*>(recv_pay) : nullptr,
+                                   argsort ? static_cast<int64_t*>(result) : nullptr, (size_t)n_recv, argsort ? gmin : 0, sort_ws,
+                                   ws_bytes, stream, reinterpret_cast<const unsigned int*>(recv_block), nranks));
+      } else if (!argsort) {
         st.set(b2s_local_sort(dtype, recv_keys, result, nullptr, (size_t)n_recv, (size_t)n_recv, 0, 1, 1, sort_ws, ws_bytes, stream));
       } else if (payb == 4 && kb != 16 && local_sort_pos32_supported((size_t)n_recv) && (size_t)n_recv < single_limit()) {
         // the radix passes carry the 32-bit payload themselves; the last one widens it

@@ -115,7 +115,7 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
 template <int KB, int XF>
 inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsigned int n,
                                int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32,
-                               const uint32_t* idx_in)
+                               const uint32_t* idx_in, const unsigned int* hist_parts, int hist_nparts)
 {
   using K            = typename KeyOf<KB>::type;
   const bool pairs   = idx_out != nullptr;
@@ -143,7 +143,11 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.n           = n;
   ra.npass       = KB;
   ra.key_bytes   = KB;
-  {
+  if (hist_parts != nullptr) {
+    // the histograms were counted elsewhere (by the ranks that sent this GPU its keys)
+    prof::Scope ps(prof::K_SCAN, stream);
+    hist_from_parts_kernel<<<1, RADIX, 0, stream>>>(ctrl, hist_parts, hist_nparts, ra);
+  } else {
     // digit histograms of all passes; the CTA that finishes last scans them and routes the passes
     prof::Scope ps(prof::K_HIST, stream);
     hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl, ra);
@@ -251,10 +255,13 @@ cudaError_t launch_radix_seg(int xf, const void* in, void* out, int64_t* idx_out
 // idx32 != 0: idx_out points to n uint32 values and receives positions 0..n-1 without the offset.
 // idx_in != null: the payload of element i is idx_in[i] instead of i (stable argsort of data that
 // already carries 32-bit payloads); the output index is index_offset + payload.
+// hist_parts != null: hist_nparts ready-made digit histograms ([part][KB][256]) to add up instead
+// of reading the keys for them.
 template <int KB>
 cudaError_t launch_radix_1d(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,
                             int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32 = 0,
-                            const uint32_t* idx_in = nullptr);
+                            const uint32_t* idx_in = nullptr, const unsigned int* hist_parts = nullptr,
+                            int hist_nparts = 0);
 
 // Segments of seg_len <= SEG_CAP elements, sorted on chip. `ctrl` must be a zeroed control block.
 template <int KB>
@@ -344,14 +351,14 @@ inline cudaError_t segsort_pairs(int xf, const void* in, void* out, int64_t* idx
   template <>                                                                                             \
   cudaError_t launch_radix_1d<KB>(int xf, const void* in, void* out, int64_t* idx_out, unsigned int n,    \
                                   int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32, \
-                                  const uint32_t* idx_in)                                                 \
+                                  const uint32_t* idx_in, const unsigned int* hp, int hn)                 \
   {                                                                                                       \
-    if (xf == XF_UNSIGNED) return radix_1d_xf<KB, XF_UNSIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
-    if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
+    if (xf == XF_UNSIGNED) return radix_1d_xf<KB, XF_UNSIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in, hp, hn); \
+    if (xf == XF_SIGNED) return radix_1d_xf<KB, XF_SIGNED>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in, hp, hn); \
     if (HAS_FLOAT && xf == XF_FLOAT)                                                                      \
-      return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
+      return radix_1d_xf<KB, (HAS_FLOAT ? XF_FLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in, hp, hn); \
     if (HAS_CFLOAT && xf == XF_CFLOAT)                                                                    \
-      return radix_1d_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in); \
+      return radix_1d_xf<KB, (HAS_CFLOAT ? XF_CFLOAT : XF_UNSIGNED)>(in, out, idx_out, n, index_offset, ws, stream, idx32, idx_in, hp, hn); \
     return cudaErrorInvalidValue;                                                                         \
   }                                                                                                       \
   template <>                                                                                             \

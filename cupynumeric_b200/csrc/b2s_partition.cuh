@@ -54,17 +54,29 @@ __device__ __forceinline__ void fp_load_splitters(FpSplit<KB>* s, const LocalSpl
 
 // number of splitters the element lies right of: three branch-free steps over the seven
 // (padded) splitters.  An invalid splitter holds the largest key and INT_MAX: nothing is right of it.
+// Most keys differ from every splitter they meet, and for those the key comparison alone decides;
+// only a key that equals one of them needs the position as well (the second, rare pass).
 template <int KB>
 __device__ __forceinline__ unsigned int fp_classify(const FpSplit<KB>* s, typename FpKey<KB>::OK k, int pos_in_tile)
 {
   unsigned int b = 0;
+  bool tie       = false;
 #pragma unroll
   for (int step = 2; step >= 0; --step) {
-    const unsigned int mid = b + (1u << step) - 1u;
-    const auto sk          = s->okey[mid];
-    const int st           = s->tie[mid];
-    const bool right       = k > sk || (k == sk && pos_in_tile > st);
-    b += right ? (1u << step) : 0u;
+    const auto sk = s->okey[b + (1u << step) - 1u];
+    tie           = tie || k == sk;
+    b += k > sk ? (1u << step) : 0u;
+  }
+  if (tie) {
+    b = 0;
+#pragma unroll
+    for (int step = 2; step >= 0; --step) {
+      const unsigned int mid = b + (1u << step) - 1u;
+      const auto sk          = s->okey[mid];
+      const int st           = s->tie[mid];
+      const bool right       = k > sk || (k == sk && pos_in_tile > st);
+      b += right ? (1u << step) : 0u;
+    }
   }
   return b;
 }
@@ -206,7 +218,10 @@ struct FpDst {
   void* pay[FP_NB];
 };
 
-template <int KB, int PAYB> struct FpSmem {
+// HIST: the CTA also counts, per destination, the digits of every radix pass of the keys it sends
+// there (the histogram pass of the receiver's local sort, done by the senders while the stores
+// wait for NVLink).
+template <int KB, int PAYB, bool HIST> struct FpSmem {
   static constexpr size_t OFF_PAY   = (size_t)FP_TILE * KB;
   static constexpr size_t OFF_SPLIT = OFF_PAY + (size_t)FP_TILE * PAYB;
   static constexpr size_t OFF_WTOT  = (OFF_SPLIT + sizeof(FpSplit<KB>) + 15) / 16 * 16;  // FP_WARPS x 2 packed words
@@ -215,20 +230,25 @@ template <int KB, int PAYB> struct FpSmem {
   static constexpr size_t OFF_DKEY  = OFF_GOFF + FP_NB * 8;
   static constexpr size_t OFF_DPAY  = OFF_DKEY + FP_NB * 8;
   static constexpr size_t OFF_BAR   = OFF_DPAY + FP_NB * 8;
-  static constexpr size_t BYTES     = OFF_BAR + 8;
+  static constexpr size_t OFF_HIST  = (OFF_BAR + 8 + 15) / 16 * 16;
+  static constexpr size_t BYTES     = OFF_HIST + (HIST ? (size_t)FP_NB * KB * RADIX * 4 : 0);
 };
 
-// Stable partition of one tile into the destinations' receive buffers (see the vote-based
-// kernel of the same role for the contract).
-template <int KB, int PAYB>
+// Stable partition of tiles into the destinations' receive buffers (see the vote-based kernel
+// of the same role for the contract).  CTA c takes tiles c, c + gridDim.x, ...: launched with one
+// CTA per tile it is the plain form; HIST launches one wave of CTAs that keep their digit counts
+// in shared memory over all of their tiles and add them to `sent_hist`
+// ([FP_NB][KB][RADIX], zeroed by the caller) at the end.
+template <int KB, int PAYB, bool HIST>
 __global__ void __launch_bounds__(FP_THREADS)
 part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long long n, int xf,
                          const LocalSplitter* __restrict__ split, const unsigned long long* __restrict__ tile_off,
                          const __grid_constant__ FpDst dst, long long global_offset, long long pay_base,
-                         unsigned int* __restrict__ status)
+                         unsigned int* __restrict__ status, unsigned int* __restrict__ sent_hist)
 {
   using Raw = typename FpKey<KB>::Raw;
-  using S   = FpSmem<KB, PAYB>;
+  using OK  = typename FpKey<KB>::OK;
+  using S   = FpSmem<KB, PAYB, HIST>;
   extern __shared__ __align__(128) unsigned char smem[];
   Raw* skeys               = reinterpret_cast<Raw*>(smem);
   unsigned char* spay      = smem + S::OFF_PAY;
@@ -239,12 +259,11 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
   void** dkey              = reinterpret_cast<void**>(smem + S::OFF_DKEY);
   void** dpay              = reinterpret_cast<void**>(smem + S::OFF_DPAY);
   uint64_t* bar            = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  unsigned int* shist      = reinterpret_cast<unsigned int*>(smem + S::OFF_HIST);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const long long base = (long long)blockIdx.x * FP_TILE;
-  fp_load_splitters<KB>(ss, split, base, tid);
+  const long long ntiles = (n + FP_TILE - 1) / FP_TILE;
   if (tid < FP_NB) {
-    goff[tid] = tile_off[(size_t)blockIdx.x * FP_NB + tid];
     dkey[tid] = dst.keys[tid];
     dpay[tid] = dst.pay[tid];
   }
@@ -252,110 +271,163 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
     mbar_init(bar, 1);
     fence_mbar_init();
   }
-  __syncthreads();
-  const int valid = (int)min((long long)FP_TILE, n - base);
-  const bool vec  = valid == FP_TILE && ((reinterpret_cast<uintptr_t>(keys + base) & 15u) == 0);
-  Raw key[FP_ITEMS];
-  const int first = tid * FP_ITEMS;
-  if (vec) {
-    // the tile arrives in the staging buffer by one bulk asynchronous copy (TMA engine); every
-    // thread then reads its 16 consecutive keys from shared memory
-    int arrived = 1;
-    if (tid == 0) {
-      mbar_expect_tx(bar, (uint32_t)(FP_TILE * KB));
-      bulk_load(skeys, keys + base, (uint32_t)(FP_TILE * KB), bar);
-      arrived = mbar_wait_bounded(bar, 0);
+  if (HIST)
+    for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) shist[i] = 0;
+  uint32_t phase = 0;
+  for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const long long base = tile * FP_TILE;
+    fp_load_splitters<KB>(ss, split, base, tid);
+    if (tid < FP_NB) goff[tid] = tile_off[(size_t)tile * FP_NB + tid];
+    __syncthreads();
+    const int valid = (int)min((long long)FP_TILE, n - base);
+    const bool vec  = valid == FP_TILE && ((reinterpret_cast<uintptr_t>(keys + base) & 15u) == 0);
+    Raw key[FP_ITEMS];
+    const int first = tid * FP_ITEMS;
+    if (vec) {
+      // the tile arrives in the staging buffer by one bulk asynchronous copy (TMA engine); every
+      // thread then reads its 16 consecutive keys from shared memory
+      int arrived = 1;
+      if (tid == 0) {
+        fence_proxy_async();  // the generic accesses of the previous tile come before the copy
+        mbar_expect_tx(bar, (uint32_t)(FP_TILE * KB));
+        bulk_load(skeys, keys + base, (uint32_t)(FP_TILE * KB), bar);
+        arrived = mbar_wait_bounded(bar, phase);
+      }
+      phase ^= 1u;
+      if (!__syncthreads_and(arrived)) {
+        if (tid == 0) atomicMax(status, DEV_ERR_TIMEOUT);  // nothing more is written by this CTA
+        return;
+      }
+      fp_load_keys<KB>(key, skeys, first, valid, true);
+    } else {
+      fp_load_keys<KB>(key, keys + base, first, valid, false);
     }
-    if (!__syncthreads_and(arrived)) {
-      if (tid == 0) atomicMax(status, DEV_ERR_TIMEOUT);  // nothing of this tile is written
-      return;
-    }
-    fp_load_keys<KB>(key, skeys, first, valid, true);
-  } else {
-    fp_load_keys<KB>(key, keys + base, first, valid, false);
-  }
 
-  // destinations of my elements (4 bits each) and my counts per destination
-  unsigned long long bs = 0, lo = 0, hi = 0;
+    // destinations of my elements (4 bits each) and my counts per destination
+    unsigned long long bs = 0, lo = 0, hi = 0;
 #pragma unroll
-  for (int i = 0; i < FP_ITEMS; ++i) {
-    const unsigned int b = fp_classify<KB>(ss, FpKey<KB>::okey(key[i], xf), first + i);
-    bs |= (unsigned long long)b << (4 * i);
-    fp_count(lo, hi, b, first + i < valid);
-  }
-  // exclusive prefix of the packed counts over the threads of the CTA (fields stay below 2^16)
-  unsigned long long ilo = lo, ihi = hi;
+    for (int i = 0; i < FP_ITEMS; ++i) {
+      const OK o           = FpKey<KB>::okey(key[i], xf);
+      const unsigned int b = fp_classify<KB>(ss, o, first + i);
+      bs |= (unsigned long long)b << (4 * i);
+      fp_count(lo, hi, b, first + i < valid);
+      if (HIST) {
+        if (valid == FP_TILE) {
+          // A digit that all 32 lanes share (constant high bytes, sorted input) would make them queue
+          // up on a few counters: then one lane per destination adds for its whole group.
+          const unsigned int same_dst = __match_any_sync(0xFFFFFFFFu, b);
+          const bool leader           = lane == __ffs(same_dst) - 1;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const unsigned long long a = __shfl_up_sync(0xFFFFFFFFu, ilo, o);
-    const unsigned long long c = __shfl_up_sync(0xFFFFFFFFu, ihi, o);
-    if (lane >= o) {
-      ilo += a;
-      ihi += c;
-    }
-  }
-  if (lane == 31) {
-    wtot[2 * warp]     = ilo;
-    wtot[2 * warp + 1] = ihi;
-  }
-  __syncthreads();
-  unsigned long long plo = ilo - lo, phi = ihi - hi, tlo = 0, thi = 0;
+          for (int p = 0; p < KB; ++p) {
+            const unsigned int d = (unsigned int)(o >> (8 * p)) & 0xFFu;
+            int same;
+            __match_all_sync(0xFFFFFFFFu, d, &same);
+            if (same) {
+              if (leader) atomicAdd(&shist[(b * KB + p) * RADIX + d], (unsigned int)__popc(same_dst));
+            } else {
+              atomicAdd(&shist[(b * KB + p) * RADIX + d], 1u);
+            }
+          }
+        } else if (first + i < valid) {
 #pragma unroll
-  for (int w = 0; w < FP_WARPS; ++w) {
-    const unsigned long long a = wtot[2 * w], c = wtot[2 * w + 1];
-    if (w < warp) {
-      plo += a;
-      phi += c;
-    }
-    tlo += a;
-    thi += c;
-  }
-  // start of every destination's piece in the staged tile: inclusive prefix over the fields by one
-  // multiplication (no field overflows: a tile holds fewer than 2^16 elements), minus the counts
-  const unsigned long long inc_lo = tlo * FP_ONES;
-  const unsigned long long inc_hi = thi * FP_ONES + (inc_lo >> 48) * FP_ONES;
-  plo += inc_lo - tlo;
-  phi += inc_hi - thi;
-  if (tid == 0) {
-#pragma unroll
-    for (int b = 0; b < FP_NB; ++b) bstart[b] = fp_field(inc_lo - tlo, inc_hi - thi, b);
-    bstart[FP_NB] = (unsigned int)valid;
-  }
-  // stage: position = start of the destination's piece + elements of lower threads + my earlier ones
-#pragma unroll
-  for (int i = 0; i < FP_ITEMS; ++i) {
-    const unsigned int b = (unsigned int)(bs >> (4 * i)) & 15u;
-    if (first + i < valid) {
-      const unsigned int p = fp_field(plo, phi, b);
-      skeys[p]             = key[i];
-      const long long g    = global_offset + base + first + i;
-      if (PAYB == 4) reinterpret_cast<uint32_t*>(spay)[p] = (uint32_t)(g - pay_base);
-      if (PAYB == 8) reinterpret_cast<int64_t*>(spay)[p] = (int64_t)g;
-    }
-    fp_count(plo, phi, b, true);
-  }
-  __syncthreads();
-  // copy-out, one destination after the other: a warp stores groups of 32 consecutive elements
-  // that start on 32-element boundaries OF THE DESTINATION, so that every store instruction fills
-  // whole 128-byte lines there (the pieces start wherever the counts put them).  Over NVLink a
-  // line written in two parts costs two packets.
-#pragma unroll 1
-  for (int b = 0; b < FP_NB; ++b) {
-    const int s0 = (int)bstart[b], len = (int)bstart[b + 1] - s0;
-    if (len <= 0) continue;
-    Raw* kdst            = static_cast<Raw*>(dkey[b]) + goff[b];
-    const int mis        = (int)((reinterpret_cast<uintptr_t>(kdst) / KB) & 31u);
-    const int groups     = (len + mis + 31) >> 5;
-    unsigned char* pdst  = PAYB ? static_cast<unsigned char*>(dpay[b]) + goff[b] * PAYB : nullptr;
-    for (int g = warp; g < groups; g += FP_WARPS) {
-      const int i = (g << 5) + lane - mis;
-      if (i >= 0 && i < len) {
-        kdst[i] = skeys[s0 + i];
-        if (PAYB == 4) reinterpret_cast<uint32_t*>(pdst)[i] = reinterpret_cast<const uint32_t*>(spay)[s0 + i];
-        if (PAYB == 8) reinterpret_cast<int64_t*>(pdst)[i] = reinterpret_cast<const int64_t*>(spay)[s0 + i];
+          for (int p = 0; p < KB; ++p) atomicAdd(&shist[(b * KB + p) * RADIX + ((unsigned int)(o >> (8 * p)) & 0xFFu)], 1u);
+        }
       }
     }
+    // exclusive prefix of the packed counts over the threads of the CTA (fields stay below 2^16)
+    unsigned long long ilo = lo, ihi = hi;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long a = __shfl_up_sync(0xFFFFFFFFu, ilo, o);
+      const unsigned long long c = __shfl_up_sync(0xFFFFFFFFu, ihi, o);
+      if (lane >= o) {
+        ilo += a;
+        ihi += c;
+      }
+    }
+    if (lane == 31) {
+      wtot[2 * warp]     = ilo;
+      wtot[2 * warp + 1] = ihi;
+    }
+    __syncthreads();
+    unsigned long long plo = ilo - lo, phi = ihi - hi, tlo = 0, thi = 0;
+#pragma unroll
+    for (int w = 0; w < FP_WARPS; ++w) {
+      const unsigned long long a = wtot[2 * w], c = wtot[2 * w + 1];
+      if (w < warp) {
+        plo += a;
+        phi += c;
+      }
+      tlo += a;
+      thi += c;
+    }
+    // start of every destination's piece in the staged tile: inclusive prefix over the fields by one
+    // multiplication (no field overflows: a tile holds fewer than 2^16 elements), minus the counts
+    const unsigned long long inc_lo = tlo * FP_ONES;
+    const unsigned long long inc_hi = thi * FP_ONES + (inc_lo >> 48) * FP_ONES;
+    plo += inc_lo - tlo;
+    phi += inc_hi - thi;
+    if (tid == 0) {
+#pragma unroll
+      for (int b = 0; b < FP_NB; ++b) bstart[b] = fp_field(inc_lo - tlo, inc_hi - thi, b);
+      bstart[FP_NB] = (unsigned int)valid;
+    }
+    // stage: position = start of the destination's piece + elements of lower threads + my earlier ones
+#pragma unroll
+    for (int i = 0; i < FP_ITEMS; ++i) {
+      const unsigned int b = (unsigned int)(bs >> (4 * i)) & 15u;
+      if (first + i < valid) {
+        const unsigned int p = fp_field(plo, phi, b);
+        skeys[p]             = key[i];
+        const long long g    = global_offset + base + first + i;
+        if (PAYB == 4) reinterpret_cast<uint32_t*>(spay)[p] = (uint32_t)(g - pay_base);
+        if (PAYB == 8) reinterpret_cast<int64_t*>(spay)[p] = (int64_t)g;
+      }
+      fp_count(plo, phi, b, true);
+    }
+    __syncthreads();
+    // copy-out, one destination after the other: a warp stores groups of 32 consecutive elements
+    // that start on 32-element boundaries OF THE DESTINATION, so that every store instruction fills
+    // whole 128-byte lines there (the pieces start wherever the counts put them).  Over NVLink a
+    // line written in two parts costs two packets.
+#pragma unroll 1
+    for (int b = 0; b < FP_NB; ++b) {
+      const int s0 = (int)bstart[b], len = (int)bstart[b + 1] - s0;
+      if (len <= 0) continue;
+      Raw* kdst            = static_cast<Raw*>(dkey[b]) + goff[b];
+      const int mis        = (int)((reinterpret_cast<uintptr_t>(kdst) / KB) & 31u);
+      const int groups     = (len + mis + 31) >> 5;
+      unsigned char* pdst  = PAYB ? static_cast<unsigned char*>(dpay[b]) + goff[b] * PAYB : nullptr;
+      for (int g = warp; g < groups; g += FP_WARPS) {
+        const int i = (g << 5) + lane - mis;
+        if (i >= 0 && i < len) {
+          kdst[i] = skeys[s0 + i];
+          if (PAYB == 4) reinterpret_cast<uint32_t*>(pdst)[i] = reinterpret_cast<const uint32_t*>(spay)[s0 + i];
+          if (PAYB == 8) reinterpret_cast<int64_t*>(pdst)[i] = reinterpret_cast<const int64_t*>(spay)[s0 + i];
+        }
+      }
+    }
+    __syncthreads();  // the tile's tables and staging buffers are free for the next tile
   }
+  if (HIST) {
+    __syncthreads();
+    for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) {
+      const unsigned int c = shist[i];
+      if (c) atomicAdd(&sent_hist[i], c);
+    }
+  }
+}
+
+// Hands every destination the digit counts of what this rank sent it: block d stores
+// sent_hist[d] ([KB][RADIX]) into destination d's landing area, slot `my_rank`.
+__global__ void hist_deliver_kernel(const unsigned int* __restrict__ sent_hist, const __grid_constant__ FpDst landing, int kb,
+                                    int my_rank)
+{
+  unsigned int* dst = static_cast<unsigned int*>(landing.keys[blockIdx.x]);
+  if (dst == nullptr) return;
+  dst += (size_t)my_rank * kb * RADIX;
+  const unsigned int* src = sent_hist + (size_t)blockIdx.x * kb * RADIX;
+  for (int i = threadIdx.x; i < kb * RADIX; i += blockDim.x) dst[i] = src[i];
 }
 
 }  // namespace b2s

@@ -108,6 +108,22 @@ __device__ __forceinline__ void scan_route_body(Ctrl* ctrl, const RouteArgs& a)
 
 static __global__ void __launch_bounds__(RADIX) scan_route_kernel(Ctrl* ctrl, RouteArgs a) { scan_route_body(ctrl, a); }
 
+// The digit histograms arrive ready-made in `nparts` pieces ([part][npass][RADIX] counts, e.g. one
+// per rank that sent this GPU keys): add them up, then scan and route as usual.  Takes the place
+// of the histogram kernel's read of all keys.
+static __global__ void __launch_bounds__(RADIX)
+hist_from_parts_kernel(Ctrl* ctrl, const unsigned int* __restrict__ parts, int nparts, RouteArgs a)
+{
+  const int d = threadIdx.x;
+  for (int p = 0; p < a.npass; ++p) {
+    unsigned int c = 0;
+    for (int s = 0; s < nparts; ++s) c += parts[((size_t)s * a.npass + p) * RADIX + d];
+    ctrl->hist[p][d] = c;
+  }
+  __syncthreads();
+  scan_route_body(ctrl, a);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel 1: digit histograms of every pass in one read of the keys.
 // Warp-level shortcut: when all 32 lanes hold the same digit (sorted input, constant high
