@@ -1119,11 +1119,15 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     for (int p = 0; p < nranks; ++p)
       if (flags[p * (sizeof(BlockB) / 8)] != B2S_OK) return (int)flags[p * (sizeof(BlockB) / 8)];
   }
-  // Direct writes with the register-counting kernels: the senders also count the digits of what
-  // they send, per destination, and hand every destination its table; the receiver's local sort
-  // then starts without reading its keys for a histogram.  (B2S_DIST_SENDER_HIST=0: off.)
+  // Direct writes with the register-counting kernels: the senders can also count the digits of
+  // what they send, per destination, and hand every destination its table; the receiver's local
+  // sort then starts without reading its keys for a histogram.  The counting costs the partition
+  // kernel more than the histogram kernel it replaces, so it pays only where that kernel waits for
+  // NVLink anyway: from 8 ranks on (7/8 of the stores leave the GPU).  B2S_DIST_SENDER_HIST=0/1
+  // overrides.
   const char* sh_env     = std::getenv("B2S_DIST_SENDER_HIST");
-  const bool sender_hist = direct && fast && !(sh_env != nullptr && sh_env[0] == '0');
+  const bool sh_wanted   = sh_env != nullptr ? sh_env[0] != '0' : nranks >= 8;
+  const bool sender_hist = direct && fast && sh_wanted;
   if (n > 0 && fast) {
     prof::Scope ps(prof::K_XCHG, stream);
     FpDst fd{};

@@ -230,7 +230,8 @@ template <int KB, int PAYB, bool HIST> struct FpSmem {
   static constexpr size_t OFF_DKEY  = OFF_GOFF + FP_NB * 8;
   static constexpr size_t OFF_DPAY  = OFF_DKEY + FP_NB * 8;
   static constexpr size_t OFF_BAR   = OFF_DPAY + FP_NB * 8;
-  static constexpr size_t OFF_HIST  = (OFF_BAR + 8 + 15) / 16 * 16;
+  static constexpr size_t OFF_WBITS = (OFF_BAR + 8 + 15) / 16 * 16;   // FP_WARPS x (or, and) of the tile's keys
+  static constexpr size_t OFF_HIST  = OFF_WBITS + FP_WARPS * 16;
   static constexpr size_t BYTES     = OFF_HIST + (HIST ? (size_t)FP_NB * KB * RADIX * 4 : 0);
 };
 
@@ -259,6 +260,7 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
   void** dkey              = reinterpret_cast<void**>(smem + S::OFF_DKEY);
   void** dpay              = reinterpret_cast<void**>(smem + S::OFF_DPAY);
   uint64_t* bar            = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  unsigned long long* wbits = reinterpret_cast<unsigned long long*>(smem + S::OFF_WBITS);
   unsigned int* shist      = reinterpret_cast<unsigned int*>(smem + S::OFF_HIST);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -305,6 +307,7 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
 
     // destinations of my elements (4 bits each) and my counts per destination
     unsigned long long bs = 0, lo = 0, hi = 0;
+    OK kor = 0, kand = (OK)~(OK)0;  // HIST: which bits differ between any two keys of the tile
 #pragma unroll
     for (int i = 0; i < FP_ITEMS; ++i) {
       const OK o           = FpKey<KB>::okey(key[i], xf);
@@ -312,26 +315,8 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
       bs |= (unsigned long long)b << (4 * i);
       fp_count(lo, hi, b, first + i < valid);
       if (HIST) {
-        if (valid == FP_TILE) {
-          // A digit that all 32 lanes share (constant high bytes, sorted input) would make them queue
-          // up on a few counters: then one lane per destination adds for its whole group.
-          const unsigned int same_dst = __match_any_sync(0xFFFFFFFFu, b);
-          const bool leader           = lane == __ffs(same_dst) - 1;
-#pragma unroll
-          for (int p = 0; p < KB; ++p) {
-            const unsigned int d = (unsigned int)(o >> (8 * p)) & 0xFFu;
-            int same;
-            __match_all_sync(0xFFFFFFFFu, d, &same);
-            if (same) {
-              if (leader) atomicAdd(&shist[(b * KB + p) * RADIX + d], (unsigned int)__popc(same_dst));
-            } else {
-              atomicAdd(&shist[(b * KB + p) * RADIX + d], 1u);
-            }
-          }
-        } else if (first + i < valid) {
-#pragma unroll
-          for (int p = 0; p < KB; ++p) atomicAdd(&shist[(b * KB + p) * RADIX + ((unsigned int)(o >> (8 * p)) & 0xFFu)], 1u);
-        }
+        kor |= o;
+        kand &= o;
       }
     }
     // exclusive prefix of the packed counts over the threads of the CTA (fields stay below 2^16)
@@ -345,9 +330,20 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
         ihi += c;
       }
     }
+    if (HIST) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        kor |= (OK)__shfl_xor_sync(0xFFFFFFFFu, kor, o);
+        kand &= (OK)__shfl_xor_sync(0xFFFFFFFFu, kand, o);
+      }
+    }
     if (lane == 31) {
       wtot[2 * warp]     = ilo;
       wtot[2 * warp + 1] = ihi;
+      if (HIST) {
+        wbits[2 * warp]     = (unsigned long long)kor;
+        wbits[2 * warp + 1] = (unsigned long long)kand;
+      }
     }
     __syncthreads();
     unsigned long long plo = ilo - lo, phi = ihi - hi, tlo = 0, thi = 0;
@@ -360,6 +356,34 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
       }
       tlo += a;
       thi += c;
+    }
+    if (HIST) {
+      // Digit counts of what this tile sends, per destination.  A byte that is the same in every key
+      // of the tile (constant high bytes, sorted input) is counted from the tile's per-destination
+      // totals; the 32 lanes of a warp would otherwise queue up on one counter per destination.
+      unsigned long long tor = 0, tand = ~0ull;
+#pragma unroll
+      for (int w = 0; w < FP_WARPS; ++w) {
+        tor |= wbits[2 * w];
+        tand &= wbits[2 * w + 1];
+      }
+      const unsigned long long varying = valid == FP_TILE ? (tor ^ tand) : ~0ull;
+#pragma unroll
+      for (int p = 0; p < KB; ++p) {
+        if ((varying >> (8 * p)) & 0xFFull) {
+#pragma unroll
+          for (int i = 0; i < FP_ITEMS; ++i) {
+            if (first + i < valid) {
+              const OK o           = FpKey<KB>::okey(key[i], xf);
+              const unsigned int b = (unsigned int)(bs >> (4 * i)) & 15u;
+              atomicAdd(&shist[(b * KB + p) * RADIX + ((unsigned int)(o >> (8 * p)) & 0xFFu)], 1u);
+            }
+          }
+        } else if (tid < FP_NB) {
+          const unsigned int c = fp_field(tlo, thi, tid);
+          if (c) atomicAdd(&shist[(tid * KB + p) * RADIX + ((unsigned int)(tor >> (8 * p)) & 0xFFu)], c);
+        }
+      }
     }
     // start of every destination's piece in the staged tile: inclusive prefix over the fields by one
     // multiplication (no field overflows: a tile holds fewer than 2^16 elements), minus the counts

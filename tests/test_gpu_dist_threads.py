@@ -162,6 +162,21 @@ def test_thread_ranks_complex_keys(cuda_device, dtype):
         check_against_global_sort(shards, argsort, res)
 
 
+@pytest.mark.parametrize("on", ["0", "1"])
+def test_thread_ranks_sender_side_histograms(cuda_device, monkeypatch, on):
+    """The senders count the digit histograms of what they send (or not): same results."""
+    monkeypatch.setenv("B2S_DIST_SENDER_HIST", on)
+    rng = np.random.default_rng(15)
+    for dtype, argsort in ((np.float32, True), (np.int64, False), (np.uint16, True), (np.float64, False)):
+        if np.dtype(dtype).kind == "f":
+            shards = [rng.standard_normal(m).astype(dtype) for m in (50_000, 20_000, 64_123, 9_000)]
+            shards[0][::97] = np.nan
+        else:
+            shards = [rng.integers(0, 1 << 12, m).astype(dtype) for m in (50_000, 20_000, 64_123, 9_000)]  # constant high bytes
+        res = run_ranks(shards, argsort)
+        check_against_global_sort(shards, argsort, res)
+
+
 def test_thread_ranks_collective_exchange_branch(cuda_device, monkeypatch):
     """B2S_DIST_P2P=0: the partition is written locally and moved with the table's exchange."""
     monkeypatch.setenv("B2S_DIST_P2P", "0")
