@@ -132,6 +132,7 @@ SIGNATURES = {
     "b2s_unique_sorted": (_I, [_I, _P, _SZ, _P, ctypes.POINTER(_SZ), _P, _SZ, _P]),
     "b2s_profile_enable": (_I, [_I]),
     "b2s_profile_read": (_I, [_I, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_ulonglong)]),
+    "b2s_profile_durations": (_I, [_I, ctypes.POINTER(ctypes.c_float), ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t)]),
     "b2s_launch_count": (ctypes.c_ulonglong, [_I]),
 }
 

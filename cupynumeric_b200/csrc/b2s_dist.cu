@@ -918,6 +918,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     int64_t* ord1 = reinterpret_cast<int64_t*>(ctl + o_ord1);
     int64_t* ord2 = reinterpret_cast<int64_t*>(ctl + o_ord2);
     int64_t* order = ord1;
+    prof::Account sample_sort_is_bookkeeping(prof::K_DIST);
     {
       prof::Scope ps(prof::K_DIST, stream);
       build_samples_kernel<<<(S_all + 255) / 256, 256, 0, stream>>>(d_allA, nranks, d_samples, khi, klo);

@@ -33,8 +33,14 @@ static cudaEvent_t take_event()
   return e;
 }
 
+static thread_local int t_account = -1;
+
+Account::Account(int kind) : saved(t_account) { t_account = kind; }
+Account::~Account() { t_account = saved; }
+
 int begin(int kind, cudaStream_t stream)
 {
+  if (t_account >= 0) kind = t_account;
   ++g_launches[kind];
   if (!g_enabled.load()) return -1;
   std::lock_guard<std::mutex> lock(g_mu);
@@ -99,6 +105,23 @@ int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches)
   }
   if (total_ms) *total_ms = tot;
   if (launches) *launches = cnt;
+  return B2S_OK;
+}
+
+int b2s_profile_durations(int kind, float* ms_out, size_t capacity, size_t* launches)
+{
+  if (kind < 0 || kind >= K_COUNT || launches == nullptr || (capacity > 0 && ms_out == nullptr)) return B2S_ERR_INVALID_ARG;
+  size_t cnt = 0;
+  std::lock_guard<std::mutex> lock(g_mu);
+  for (auto& r : g_recs) {
+    if (r.kind != kind) continue;
+    if (cnt < capacity) {
+      if (cudaEventSynchronize(r.b) != cudaSuccess) return B2S_ERR_CUDA;
+      if (cudaEventElapsedTime(&ms_out[cnt], r.a, r.b) != cudaSuccess) return B2S_ERR_CUDA;
+    }
+    ++cnt;
+  }
+  *launches = cnt;
   return B2S_OK;
 }
 

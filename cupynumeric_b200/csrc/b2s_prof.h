@@ -23,6 +23,15 @@ enum Kind : int {
 int begin(int kind, cudaStream_t stream);
 void end(int id, cudaStream_t stream);
 
+// While one of these lives, every launch of the calling thread is accounted under `kind` whatever
+// its Scope says (the sort of the gathered samples belongs to the distributed sort's bookkeeping,
+// not to the radix passes over the data).
+struct Account {
+  int saved;
+  explicit Account(int kind);
+  ~Account();
+};
+
 struct Scope {
   int id;
   cudaStream_t stream;

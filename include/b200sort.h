@@ -346,6 +346,12 @@ int b2s_profile_enable(int on);
  * b2s_profile_enable(1).  Waits for the recorded launches to finish. */
 int b2s_profile_read(int kind, double* total_ms, unsigned long long* launches);
 
+/* The same records one by one, in launch order: writes the durations (ms) of the first `capacity`
+ * launches of the family to ms_out and the number of recorded launches to *launches (call with
+ * capacity 0 to size the array).  A radix pass that the routing found it could skip still shows
+ * up here, as a launch of a few microseconds. */
+int b2s_profile_durations(int kind, float* ms_out, size_t capacity, size_t* launches);
+
 /* Number of kernels of one family (or of all, kind < 0) this process has launched so far. */
 unsigned long long b2s_launch_count(int kind);
 
