@@ -2,12 +2,17 @@
 // here): lexicographic (real, imaginary) order, the order the reference's Thrust path
 // uses for complex64/128 (src/cupynumeric/sort/thrust_sort.cuh:61-123 with the comparison of
 // src/cupynumeric/binary/binary_op_util.h:32-36).  Done as two stable radix argsorts - by the
-// imaginary parts, then by the real parts in that order - which is the lexicographic order.
+// imaginary parts, then by the real parts in that order - which is the lexicographic order.  On
+// 1-D tiles the order found by the first sort rides through the passes of the second one as a
+// 32-bit payload (no 64-bit indices in any pass, no composition of two permutations).
 #include "../../include/b200sort.h"
 #include "b2s_common.cuh"
 #include "b2s_prof.h"
 
 namespace b2s {
+bool local_sort_pos32_supported(size_t n);
+int local_sort_payload32(int dtype, const void* keys_in, const uint32_t* pay_in, int64_t* idx_out, size_t n,
+                         int64_t index_offset, void* ws, size_t ws_bytes, cudaStream_t stream, int out32 = 0);
 
 template <typename F>
 __global__ void cplx_split_kernel(const F* __restrict__ c, F* __restrict__ re, F* __restrict__ im, size_t n)
@@ -25,6 +30,50 @@ __global__ void cplx_gather_kernel(const F* __restrict__ src, const int64_t* __r
 {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = src[i / seg * seg + (size_t)idx[i]];
+}
+
+// 1-D, 32-bit positions: out[i] = src[pos[i]]
+template <typename F>
+__global__ void cplx_gather32_kernel(const F* __restrict__ src, const uint32_t* __restrict__ pos, F* __restrict__ out, size_t n)
+{
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = src[pos[i]];
+}
+
+// 1-D, 32-bit positions of the final order: the indices and/or the sorted complex values.  The
+// values come from the interleaved input, one 16-byte access per element when VEC (input and
+// output 16-byte aligned), which touches half the sectors of two 8-byte gathers.
+template <typename F, bool VEC>
+__global__ void cplx_finish32_kernel(const F* __restrict__ c_in, const uint32_t* __restrict__ pos, F* __restrict__ c_out,
+                                     int64_t* __restrict__ idx_out, size_t n, int64_t index_offset)
+{
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t j = pos[i];
+    if (idx_out) idx_out[i] = (int64_t)j + index_offset;
+    if (c_out) {
+      if (VEC) {
+        reinterpret_cast<double2*>(c_out)[i] = __ldg(reinterpret_cast<const double2*>(c_in) + j);
+      } else {
+        c_out[2 * i]     = c_in[2 * j];
+        c_out[2 * i + 1] = c_in[2 * j + 1];
+      }
+    }
+  }
+}
+
+// the same from the split copies (the sort is in place: the interleaved input is being overwritten)
+template <typename F>
+__global__ void cplx_finish_split32_kernel(const F* __restrict__ re, const F* __restrict__ im, const uint32_t* __restrict__ pos,
+                                           F* __restrict__ c_out, int64_t* __restrict__ idx_out, size_t n, int64_t index_offset)
+{
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t j = pos[i];
+    if (idx_out) idx_out[i] = (int64_t)j + index_offset;
+    if (c_out) {
+      c_out[2 * i]     = re[j];
+      c_out[2 * i + 1] = im[j];
+    }
+  }
 }
 
 // Composes the two permutations and writes the indices and/or the sorted complex values.
@@ -92,6 +141,30 @@ static int complex_sort_t(int dtype, const void* keys_in, void* keys_out, int64_
   {
     prof::Scope ps(prof::K_FIXUP, stream);
     cplx_split_kernel<F><<<grid, 256, 0, stream>>>(static_cast<const F*>(keys_in), re, im, volume);
+  }
+  if (one_d && local_sort_pos32_supported(volume)) {
+    uint32_t* pos1 = reinterpret_cast<uint32_t*>(idx1);
+    uint32_t* pos2 = reinterpret_cast<uint32_t*>(idx2);
+    rc = local_sort_payload32(part, im, nullptr, reinterpret_cast<int64_t*>(pos1), volume, 0, ws, l.inner, stream, 1);
+    if (rc != B2S_OK) return rc;
+    {
+      prof::Scope ps(prof::K_FIXUP, stream);
+      cplx_gather32_kernel<F><<<grid, 256, 0, stream>>>(re, pos1, re1, volume);
+    }
+    rc = local_sort_payload32(part, re1, pos1, reinterpret_cast<int64_t*>(pos2), volume, 0, ws, l.inner, stream, 1);
+    if (rc != B2S_OK) return rc;
+    {
+      prof::Scope ps(prof::K_FIXUP, stream);
+      // in place (keys_out == keys_in) the values are taken from the split copies instead
+      const bool vec = sizeof(F) == 8 && keys_out != keys_in && ((reinterpret_cast<uintptr_t>(keys_in) | reinterpret_cast<uintptr_t>(keys_out)) & 15u) == 0;
+      if (keys_out == keys_in)
+        cplx_finish_split32_kernel<F><<<grid, 256, 0, stream>>>(re, im, pos2, static_cast<F*>(keys_out), idx_out, volume, index_offset);
+      else if (vec)
+        cplx_finish32_kernel<F, true><<<grid, 256, 0, stream>>>(static_cast<const F*>(keys_in), pos2, static_cast<F*>(keys_out), idx_out, volume, index_offset);
+      else
+        cplx_finish32_kernel<F, false><<<grid, 256, 0, stream>>>(static_cast<const F*>(keys_in), pos2, static_cast<F*>(keys_out), idx_out, volume, index_offset);
+    }
+    return cudaGetLastError() == cudaSuccess ? B2S_OK : B2S_ERR_CUDA;
   }
   rc = b2s_local_sort(part, im, nullptr, idx1, volume, segment, 0, one_d, 1, ws, l.inner, stream);
   if (rc != B2S_OK) return rc;

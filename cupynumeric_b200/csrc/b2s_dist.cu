@@ -824,6 +824,11 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
   const int nb  = nranks;
   // up to 8 destinations and keys of at most 8 bytes: the register-counting partition kernels
   const bool fast = nb <= FP_NB && kb <= 8;
+  // With the register-counting kernels the counting pass can also count, per destination, the digits
+  // of the keys it will send there; every destination gets the tables of what it receives and its
+  // local sort starts without reading its keys for a histogram (B2S_DIST_SENDER_HIST=0/1).
+  const char* sh_env    = std::getenv("B2S_DIST_SENDER_HIST");
+  const bool count_hist = fast && nranks > 1 && (sh_env != nullptr ? sh_env[0] == '1' : true);
   int nbp         = 1;
   while (nbp < nb) nbp <<= 1;                       // padded bucket count
   if (fast) nbp = FP_NB;
@@ -949,7 +954,23 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     if (n > 0) {
       {
         prof::Scope ps(prof::K_DIST, stream);
-        if (fast) {
+        if (fast && count_hist) {
+          by_width(kb, [&](auto w) {
+            constexpr int KB     = decltype(w)::value;
+            constexpr size_t TAB = (size_t)FP_NB * KB * RADIX * 4;
+            auto kern            = part_count_hist_kernel<KB>;
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TAB);
+            if (e != cudaSuccess) return e;
+            int dev = 0, sms = 148, per_sm = 1;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, FP_THREADS, TAB);
+            const long long grid = std::min<long long>(ntiles, (long long)sms * (per_sm < 1 ? 1 : per_sm));
+            kern<<<(unsigned int)grid, FP_THREADS, TAB, stream>>>(static_cast<const typename FpKey<KB>::Raw*>(keys_in), n, ntiles, xf,
+                                                                    d_local, d_counts, d_chunks, d_sent);
+            return cudaGetLastError();
+          });
+        } else if (fast) {
           by_width(kb, [&](auto w) {
             constexpr int KB = decltype(w)::value;
             part_count_fast_kernel<KB><<<(unsigned int)ntiles, FP_THREADS, 0, stream>>>(
@@ -1120,15 +1141,7 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
     for (int p = 0; p < nranks; ++p)
       if (flags[p * (sizeof(BlockB) / 8)] != B2S_OK) return (int)flags[p * (sizeof(BlockB) / 8)];
   }
-  // Direct writes with the register-counting kernels: the senders can also count the digits of
-  // what they send, per destination, and hand every destination its table, so that the receiver's
-  // local sort starts without reading its keys for a histogram.  Off unless B2S_DIST_SENDER_HIST=1:
-  // measured on 8 GPUs (2^28 keys each) the counting slows the partition kernel by more than the
-  // histogram pass it saves (float32 + index: 4.19 vs 2.85 + 0.49 ms; int64: 3.68 vs 2.56 + 1.11 ms) -
-  // its shared-memory tables cut the CTAs per SM, and with them the stores in flight to NVLink.
-  const char* sh_env     = std::getenv("B2S_DIST_SENDER_HIST");
-  const bool sh_wanted   = sh_env != nullptr && sh_env[0] == '1';
-  const bool sender_hist = direct && fast && sh_wanted;
+  const bool sender_hist = direct && count_hist;  // the tables were counted by the counting pass
   if (n > 0 && fast) {
     prof::Scope ps(prof::K_XCHG, stream);
     FpDst fd{};
@@ -1154,11 +1167,6 @@ int b2s_dist_sort_1d_ops(int dtype, const void* keys_in, size_t n_local, int64_t
                                                                   (long long)global_offset, gmin, d_status, d_sent);
         return cudaGetLastError();
       };
-      if (sender_hist) {
-        if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0, true>, FpSmem<KB, 0, true>::BYTES, true);
-        if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4, true>, FpSmem<KB, 4, true>::BYTES, true);
-        return launch(part_scatter_fast_kernel<KB, 8, true>, FpSmem<KB, 8, true>::BYTES, true);
-      }
       if (payb == 0) return launch(part_scatter_fast_kernel<KB, 0, false>, FpSmem<KB, 0, false>::BYTES, false);
       if (payb == 4) return launch(part_scatter_fast_kernel<KB, 4, false>, FpSmem<KB, 4, false>::BYTES, false);
       return launch(part_scatter_fast_kernel<KB, 8, false>, FpSmem<KB, 8, false>::BYTES, false);

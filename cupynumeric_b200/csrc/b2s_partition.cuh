@@ -25,18 +25,26 @@ template <int KB> struct FpKey {
 };
 
 // The splitters of one tile in shared memory: ordered key and the tile-relative position that
-// breaks ties (-1: every equal key lies right of the splitter; INT_MAX: none does).
+// breaks ties (-1: every equal key lies right of the splitter; INT_MAX: none does).  Only the tile
+// that holds a splitter's own element has a tie position inside it; for every other tile "right of
+// the splitter" is a comparison of keys alone, k > adj with adj = key - 1 where the equal keys lie
+// right.  `simple` says that all seven comparisons of this tile can be made that way.
 template <int KB> struct FpSplit {
   typename FpKey<KB>::OK okey[FP_NB];
+  typename FpKey<KB>::OK adj[FP_NB];
   int tie[FP_NB];
+  int simple;
 };
 
+// Called by all threads of the CTA; the caller's __syncthreads() comes after it.  `simple` is
+// cleared by the last __syncthreads() user of the previous tile at the earliest, set here by
+// thread FP_NB and lowered by threads 0..FP_NB-1 after a barrier of their warp.
 template <int KB>
 __device__ __forceinline__ void fp_load_splitters(FpSplit<KB>* s, const LocalSplitter* __restrict__ split, long long tile_base,
                                                   int tid)
 {
   using OK = typename FpKey<KB>::OK;
-  if (tid < FP_NB) {
+  if (tid < 32) {
     OK k  = (OK)~(OK)0;
     int t = 0x7FFFFFFF;
     if (tid < FP_NB - 1) {
@@ -47,16 +55,20 @@ __device__ __forceinline__ void fp_load_splitters(FpSplit<KB>* s, const LocalSpl
         t                  = rel < 0 ? -1 : (rel > 0x7FFFFFFFll ? 0x7FFFFFFF : (int)rel);
       }
     }
-    s->okey[tid] = k;
-    s->tie[tid]  = t;
+    // equal keys all right (t < 0, needs key - 1 to exist) or all left (t beyond the tile)
+    const bool plain = t < 0 ? k != (OK)0 : t >= FP_TILE - 1;
+    const bool all   = __all_sync(0xFFFFFFFFu, tid >= FP_NB || plain);
+    if (tid < FP_NB) {
+      s->okey[tid] = k;
+      s->adj[tid]  = t < 0 ? (OK)(k - (OK)1) : k;
+      s->tie[tid]  = t;
+    }
+    if (tid == 0) s->simple = all ? 1 : 0;
   }
 }
 
 // number of splitters the element lies right of: three branch-free steps over the seven
 // (padded) splitters.  An invalid splitter holds the largest key and INT_MAX: nothing is right of it.
-// (Deciding by the key alone and looking at positions only for keys that equal a splitter saves
-// 0.07 ms per 2^28 random keys and costs 0.25 ms on heavily duplicated ones, where every warp holds
-// such a key: measured, not adopted.)
 template <int KB>
 __device__ __forceinline__ unsigned int fp_classify(const FpSplit<KB>* s, typename FpKey<KB>::OK k, int pos_in_tile)
 {
@@ -69,6 +81,16 @@ __device__ __forceinline__ unsigned int fp_classify(const FpSplit<KB>* s, typena
     const bool right       = k > sk || (k == sk && pos_in_tile > st);
     b += right ? (1u << step) : 0u;
   }
+  return b;
+}
+
+// the same for a tile whose FpSplit is `simple`: keys alone decide
+template <int KB>
+__device__ __forceinline__ unsigned int fp_classify_simple(const FpSplit<KB>* s, typename FpKey<KB>::OK k)
+{
+  unsigned int b = 0;
+#pragma unroll
+  for (int step = 2; step >= 0; --step) b += k > s->adj[b + (1u << step) - 1u] ? (1u << step) : 0u;
   return b;
 }
 
@@ -141,12 +163,20 @@ part_count_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long lo
     const uint4* v = reinterpret_cast<const uint4*>(keys + base);
 #pragma unroll
     for (int j = 0; j < NV; ++j) u[j].q = __ldg(v + j * FP_THREADS + tid);
+    if (ss.simple) {  // the same for the whole CTA
 #pragma unroll
-    for (int j = 0; j < NV; ++j) {
+      for (int j = 0; j < NV; ++j) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        const int e = (j * FP_THREADS + tid) * VEC + k;
-        fp_count(lo, hi, fp_classify<KB>(&ss, FpKey<KB>::okey(u[j].r[k], xf), e), true);
+        for (int k = 0; k < VEC; ++k) fp_count(lo, hi, fp_classify_simple<KB>(&ss, FpKey<KB>::okey(u[j].r[k], xf)), true);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const int e = (j * FP_THREADS + tid) * VEC + k;
+          fp_count(lo, hi, fp_classify<KB>(&ss, FpKey<KB>::okey(u[j].r[k], xf), e), true);
+        }
       }
     }
   } else {
@@ -171,6 +201,126 @@ part_count_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long lo
     const unsigned int c = cnt[tid];
     tile_counts[(size_t)blockIdx.x * FP_NB + tid] = c;
     if (c) atomicAdd(&chunk_sums[(size_t)(blockIdx.x / FP_CHUNK_TILES) * FP_NB + tid], (unsigned long long)c);
+  }
+}
+
+// The counting pass that also counts, per destination, the digits of every radix pass of the keys
+// it will send there: the histogram pass of the receivers' local sorts, done where the keys are in
+// registers anyway (the classification keeps the ALU pipe busy, the counters the shared-memory
+// pipe).  One wave of CTAs, each over tiles c, c + gridDim.x, ...; the tables stay in shared
+// memory over all tiles of the CTA and are added to sent_hist[(dest * KB + byte) * 256 + digit] once.
+// A byte that is the same in every key of a tile (constant high bytes, sorted input) is counted from
+// the tile's per-destination totals: the lanes of a warp would otherwise queue up on one counter.
+template <int KB>
+__global__ void __launch_bounds__(FP_THREADS)
+part_count_hist_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long long n, long long ntiles, int xf,
+                       const LocalSplitter* __restrict__ split, unsigned int* __restrict__ tile_counts,
+                       unsigned long long* __restrict__ chunk_sums, unsigned int* __restrict__ sent_hist)
+{
+  using Raw = typename FpKey<KB>::Raw;
+  using OK  = typename FpKey<KB>::OK;
+  extern __shared__ __align__(16) unsigned char fp_count_smem[];
+  unsigned int* shist = reinterpret_cast<unsigned int*>(fp_count_smem);  // FP_NB * KB * RADIX
+  __shared__ FpSplit<KB> ss;
+  __shared__ unsigned long long wtot[2 * FP_WARPS], wbits[2 * FP_WARPS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int VEC = 16 / KB;         // keys per 16-byte vector
+  constexpr int NV  = FP_ITEMS / VEC;  // vectors per thread
+  for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) shist[i] = 0;
+  for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const long long base = tile * FP_TILE;
+    fp_load_splitters<KB>(&ss, split, base, tid);
+    __syncthreads();
+    const int valid = (int)min((long long)FP_TILE, n - base);
+    const bool vec  = valid == FP_TILE && ((reinterpret_cast<uintptr_t>(keys + base) & 15u) == 0);
+    union {
+      uint4 q;
+      Raw r[VEC];
+    } u[NV];
+    if (vec) {
+      const uint4* v = reinterpret_cast<const uint4*>(keys + base);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) u[j].q = __ldg(v + j * FP_THREADS + tid);
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const int e = (j * FP_THREADS + tid) * VEC + k;
+          u[j].r[k]   = e < valid ? keys[base + e] : (Raw)0;
+        }
+      }
+    }
+    unsigned long long bs = 0, lo = 0, hi = 0;
+    OK kor = 0, kand = (OK)~(OK)0;
+    const bool simple = ss.simple != 0;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const int e          = (j * FP_THREADS + tid) * VEC + k;
+        const OK o           = FpKey<KB>::okey(u[j].r[k], xf);
+        const unsigned int b = simple ? fp_classify_simple<KB>(&ss, o) : fp_classify<KB>(&ss, o, e);
+        bs |= (unsigned long long)b << (4 * (j * VEC + k));
+        fp_count(lo, hi, b, e < valid);
+        kor |= o;
+        kand &= o;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lo += __shfl_xor_sync(0xFFFFFFFFu, lo, o);
+      hi += __shfl_xor_sync(0xFFFFFFFFu, hi, o);
+      kor |= (OK)__shfl_xor_sync(0xFFFFFFFFu, kor, o);
+      kand &= (OK)__shfl_xor_sync(0xFFFFFFFFu, kand, o);
+    }
+    if (lane == 0) {
+      wtot[2 * warp]      = lo;
+      wtot[2 * warp + 1]  = hi;
+      wbits[2 * warp]     = (unsigned long long)kor;
+      wbits[2 * warp + 1] = (unsigned long long)kand;
+    }
+    __syncthreads();
+    unsigned long long tlo = 0, thi = 0, tor = 0, tand = ~0ull;
+#pragma unroll
+    for (int w = 0; w < FP_WARPS; ++w) {
+      tlo += wtot[2 * w];
+      thi += wtot[2 * w + 1];
+      tor |= wbits[2 * w];
+      tand &= wbits[2 * w + 1];
+    }
+    if (tid < FP_NB) {
+      const unsigned int c = fp_field(tlo, thi, tid);
+      tile_counts[(size_t)tile * FP_NB + tid] = c;
+      if (c) atomicAdd(&chunk_sums[(size_t)(tile / FP_CHUNK_TILES) * FP_NB + tid], (unsigned long long)c);
+    }
+    const unsigned long long varying = valid == FP_TILE ? (tor ^ tand) : ~0ull;
+#pragma unroll
+    for (int p = 0; p < KB; ++p) {
+      if ((varying >> (8 * p)) & 0xFFull) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            const int e = (j * FP_THREADS + tid) * VEC + k;
+            if (e < valid) {
+              const OK o           = FpKey<KB>::okey(u[j].r[k], xf);
+              const unsigned int b = (unsigned int)(bs >> (4 * (j * VEC + k))) & 15u;
+              atomicAdd(&shist[(b * KB + p) * RADIX + ((unsigned int)(o >> (8 * p)) & 0xFFu)], 1u);
+            }
+          }
+        }
+      } else if (tid < FP_NB) {
+        const unsigned int c = fp_field(tlo, thi, tid);
+        if (c) atomicAdd(&shist[(tid * KB + p) * RADIX + ((unsigned int)(tor >> (8 * p)) & 0xFFu)], c);
+      }
+    }
+    __syncthreads();  // the splitters and the warps' words are free for the next tile
+  }
+  __syncthreads();
+  for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) {
+    const unsigned int c = shist[i];
+    if (c) atomicAdd(&sent_hist[i], c);
   }
 }
 
@@ -299,15 +449,29 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
     // destinations of my elements (4 bits each) and my counts per destination
     unsigned long long bs = 0, lo = 0, hi = 0;
     OK kor = 0, kand = (OK)~(OK)0;  // HIST: which bits differ between any two keys of the tile
+    if (ss->simple) {  // the same for the whole CTA
 #pragma unroll
-    for (int i = 0; i < FP_ITEMS; ++i) {
-      const OK o           = FpKey<KB>::okey(key[i], xf);
-      const unsigned int b = fp_classify<KB>(ss, o, first + i);
-      bs |= (unsigned long long)b << (4 * i);
-      fp_count(lo, hi, b, first + i < valid);
-      if (HIST) {
-        kor |= o;
-        kand &= o;
+      for (int i = 0; i < FP_ITEMS; ++i) {
+        const OK o           = FpKey<KB>::okey(key[i], xf);
+        const unsigned int b = fp_classify_simple<KB>(ss, o);
+        bs |= (unsigned long long)b << (4 * i);
+        fp_count(lo, hi, b, first + i < valid);
+        if (HIST) {
+          kor |= o;
+          kand &= o;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < FP_ITEMS; ++i) {
+        const OK o           = FpKey<KB>::okey(key[i], xf);
+        const unsigned int b = fp_classify<KB>(ss, o, first + i);
+        bs |= (unsigned long long)b << (4 * i);
+        fp_count(lo, hi, b, first + i < valid);
+        if (HIST) {
+          kor |= o;
+          kand &= o;
+        }
       }
     }
     // exclusive prefix of the packed counts over the threads of the CTA (fields stay below 2^16)
