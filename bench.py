@@ -564,22 +564,67 @@ class Bench:
                                       "algorithmic_bytes_per_launch": c["sweep_bytes"] * n_local,
                                       "traffic": traffic * n_local if traffic else None}
         if nranks == 1 and not args.no_cub:
-            rec["cub_baseline"] = self.cub_baseline(tile, c["argsort"])
+            rec["cub_baseline"] = self.cub_baseline(tile, c["argsort"], flush)
         rec["_clocks"], rec["_launches"], rec["_tile"] = clocks, launches, tile
         return rec
 
-    def cub_baseline(self, tile, argsort):
-        """The CCCL library sort the reference's GPU variant calls, on the same tile."""
+    def cub_baseline(self, tile, argsort, flush):
+        """The CCCL library sort the reference's GPU variant calls, on the same tile, under the same
+        cache protocol as the timed steps (L2 flushed before every step when the input fits L2)."""
         try:
             from oracle import cub_baseline as cb
             if not cb.available():
                 return {"unavailable": "oracle/libcub_baseline.so is not built"}
-            ms, _ = cb.time_sort(tile, argsort,
-                                 steps=max(1, min(self.args.steps, 5)), warmup=2)
+            ms, _ = cb.time_sort(tile, argsort, steps=max(1, min(self.args.steps, 5)), warmup=2,
+                                 between=self.flush_l2 if flush else None)
+            ours = self.direct_call_ms(tile, argsort, flush, steps=max(1, min(self.args.steps, 5)), warmup=2)
             return {"ms_per_step": ms, "gkeys_per_s": tile.numel() / (ms * 1e-3) / 1e9,
+                    "ours_same_protocol_ms": ours,
+                    "l2": "flushed before every step" if flush else "input larger than L2",
+                    "timed": "direct C call with preallocated buffers (no allocation, no Python dispatch inside the interval)",
                     "what": "cub::DeviceRadixSort / DeviceSegmentedRadixSort (+ index fill for argsort), CCCL of the CUDA toolkit"}
         except Exception as e:  # the baseline is optional evidence, not part of the product
             return {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+
+    def direct_call_ms(self, tile, argsort, flush, steps, warmup):
+        """b2s_local_sort timed the way the library baseline is: the C entry point itself, output and
+        workspace allocated beforehand."""
+        torch, lib = self.torch, self.lib
+        from cupynumeric_b200 import _lib
+        from cupynumeric_b200._thunk.deferred import to_numpy_dtype
+        code = _lib.DTYPE_CODE[to_numpy_dtype(tile.dtype)]
+        volume, segment = tile.numel(), tile.shape[-1]
+        need = ctypes.c_size_t(0)
+        _lib.check(lib.b2s_workspace_bytes(code, volume, segment, int(argsort), ctypes.byref(need)), "b2s_workspace_bytes")
+        ws = torch.empty(max(need.value, 256), dtype=torch.uint8, device=tile.device)
+        out = torch.empty(tile.shape, dtype=torch.int64 if argsort else tile.dtype, device=tile.device)
+        stream = torch.cuda.current_stream().cuda_stream
+
+        def call():
+            _lib.check(lib.b2s_local_sort(code, tile.data_ptr(), None if argsort else out.data_ptr(),
+                                          out.data_ptr() if argsort else None, volume, segment, 0, int(tile.ndim == 1), 1,
+                                          ws.data_ptr(), ws.numel(), stream), "b2s_local_sort")
+
+        for _ in range(warmup):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if flush:
+            ms = 0.0
+            for _ in range(steps):
+                self.flush_l2()
+                e0.record()
+                call()
+                e1.record()
+                torch.cuda.synchronize()
+                ms += e0.elapsed_time(e1)
+            return ms / steps
+        e0.record()
+        for _ in range(steps):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
 
     def run_e2e(self, name, log2, tile):
         """The same step through the public API with pinned host buffers on both sides."""

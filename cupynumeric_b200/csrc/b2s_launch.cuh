@@ -122,7 +122,9 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   const auto lay     = radix_1d_layout<KB>(n, pairs);
   Ctrl* ctrl         = reinterpret_cast<Ctrl*>(ws);
   unsigned int* lb   = reinterpret_cast<unsigned int*>(ws + lay.off_lookback);
-  cudaError_t e      = cudaMemsetAsync(ws, 0, lay.off_keys[0], stream);  // control block + look-back table
+  // control block; the look-back tables too unless the histogram kernel clears them
+  const bool own_hist = hist_parts == nullptr;
+  cudaError_t e       = cudaMemsetAsync(ws, 0, own_hist ? lay.off_lookback : lay.off_keys[0], stream);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -143,6 +145,8 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   ra.n           = n;
   ra.npass       = KB;
   ra.key_bytes   = KB;
+  ra.zero_ptr    = own_hist ? reinterpret_cast<uint4*>(ws + lay.off_lookback) : nullptr;
+  ra.zero_vecs   = own_hist ? (lay.off_keys[0] - lay.off_lookback) / 16 : 0;
   if (hist_parts != nullptr) {
     // the histograms were counted elsewhere (by the ranks that sent this GPU its keys)
     prof::Scope ps(prof::K_SCAN, stream);

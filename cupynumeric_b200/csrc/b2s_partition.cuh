@@ -359,10 +359,7 @@ struct FpDst {
   void* pay[FP_NB];
 };
 
-// HIST: the CTA also counts, per destination, the digits of every radix pass of the keys it sends
-// there (the histogram pass of the receiver's local sort, done by the senders while the stores
-// wait for NVLink).
-template <int KB, int PAYB, bool HIST> struct FpSmem {
+template <int KB, int PAYB> struct FpSmem {
   static constexpr size_t OFF_PAY   = (size_t)FP_TILE * KB;
   static constexpr size_t OFF_SPLIT = OFF_PAY + (size_t)FP_TILE * PAYB;
   static constexpr size_t OFF_WTOT  = (OFF_SPLIT + sizeof(FpSplit<KB>) + 15) / 16 * 16;  // FP_WARPS x 2 packed words
@@ -371,26 +368,22 @@ template <int KB, int PAYB, bool HIST> struct FpSmem {
   static constexpr size_t OFF_DKEY  = OFF_GOFF + FP_NB * 8;
   static constexpr size_t OFF_DPAY  = OFF_DKEY + FP_NB * 8;
   static constexpr size_t OFF_BAR   = OFF_DPAY + FP_NB * 8;
-  static constexpr size_t OFF_WBITS = (OFF_BAR + 8 + 15) / 16 * 16;   // FP_WARPS x (or, and) of the tile's keys
-  static constexpr size_t OFF_HIST  = OFF_WBITS + FP_WARPS * 16;
-  static constexpr size_t BYTES     = OFF_HIST + (HIST ? (size_t)FP_NB * KB * RADIX * 4 : 0);
+  static constexpr size_t BYTES     = OFF_BAR + 8;
 };
 
 // Stable partition of tiles into the destinations' receive buffers (see the vote-based kernel
-// of the same role for the contract).  CTA c takes tiles c, c + gridDim.x, ...: launched with one
-// CTA per tile it is the plain form; HIST launches one wave of CTAs that keep their digit counts
-// in shared memory over all of their tiles and add them to `sent_hist`
-// ([FP_NB][KB][RADIX], zeroed by the caller) at the end.
-template <int KB, int PAYB, bool HIST>
+// of the same role for the contract).  CTA c takes tiles c, c + gridDim.x, ...; launched with one
+// CTA per tile.
+template <int KB, int PAYB>
 __global__ void __launch_bounds__(FP_THREADS)
 part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long long n, int xf,
                          const LocalSplitter* __restrict__ split, const unsigned long long* __restrict__ tile_off,
                          const __grid_constant__ FpDst dst, long long global_offset, long long pay_base,
-                         unsigned int* __restrict__ status, unsigned int* __restrict__ sent_hist)
+                         unsigned int* __restrict__ status)
 {
   using Raw = typename FpKey<KB>::Raw;
   using OK  = typename FpKey<KB>::OK;
-  using S   = FpSmem<KB, PAYB, HIST>;
+  using S   = FpSmem<KB, PAYB>;
   extern __shared__ __align__(128) unsigned char smem[];
   Raw* skeys               = reinterpret_cast<Raw*>(smem);
   unsigned char* spay      = smem + S::OFF_PAY;
@@ -401,8 +394,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
   void** dkey              = reinterpret_cast<void**>(smem + S::OFF_DKEY);
   void** dpay              = reinterpret_cast<void**>(smem + S::OFF_DPAY);
   uint64_t* bar            = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
-  unsigned long long* wbits = reinterpret_cast<unsigned long long*>(smem + S::OFF_WBITS);
-  unsigned int* shist      = reinterpret_cast<unsigned int*>(smem + S::OFF_HIST);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long ntiles = (n + FP_TILE - 1) / FP_TILE;
@@ -414,8 +405,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
     mbar_init(bar, 1);
     fence_mbar_init();
   }
-  if (HIST)
-    for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) shist[i] = 0;
   uint32_t phase = 0;
   for (long long tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const long long base = tile * FP_TILE;
@@ -448,7 +437,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
 
     // destinations of my elements (4 bits each) and my counts per destination
     unsigned long long bs = 0, lo = 0, hi = 0;
-    OK kor = 0, kand = (OK)~(OK)0;  // HIST: which bits differ between any two keys of the tile
     if (ss->simple) {  // the same for the whole CTA
 #pragma unroll
       for (int i = 0; i < FP_ITEMS; ++i) {
@@ -456,10 +444,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
         const unsigned int b = fp_classify_simple<KB>(ss, o);
         bs |= (unsigned long long)b << (4 * i);
         fp_count(lo, hi, b, first + i < valid);
-        if (HIST) {
-          kor |= o;
-          kand &= o;
-        }
       }
     } else {
 #pragma unroll
@@ -468,10 +452,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
         const unsigned int b = fp_classify<KB>(ss, o, first + i);
         bs |= (unsigned long long)b << (4 * i);
         fp_count(lo, hi, b, first + i < valid);
-        if (HIST) {
-          kor |= o;
-          kand &= o;
-        }
       }
     }
     // exclusive prefix of the packed counts over the threads of the CTA (fields stay below 2^16)
@@ -485,20 +465,9 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
         ihi += c;
       }
     }
-    if (HIST) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        kor |= (OK)__shfl_xor_sync(0xFFFFFFFFu, kor, o);
-        kand &= (OK)__shfl_xor_sync(0xFFFFFFFFu, kand, o);
-      }
-    }
     if (lane == 31) {
       wtot[2 * warp]     = ilo;
       wtot[2 * warp + 1] = ihi;
-      if (HIST) {
-        wbits[2 * warp]     = (unsigned long long)kor;
-        wbits[2 * warp + 1] = (unsigned long long)kand;
-      }
     }
     __syncthreads();
     unsigned long long plo = ilo - lo, phi = ihi - hi, tlo = 0, thi = 0;
@@ -511,34 +480,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
       }
       tlo += a;
       thi += c;
-    }
-    if (HIST) {
-      // Digit counts of what this tile sends, per destination.  A byte that is the same in every key
-      // of the tile (constant high bytes, sorted input) is counted from the tile's per-destination
-      // totals; the 32 lanes of a warp would otherwise queue up on one counter per destination.
-      unsigned long long tor = 0, tand = ~0ull;
-#pragma unroll
-      for (int w = 0; w < FP_WARPS; ++w) {
-        tor |= wbits[2 * w];
-        tand &= wbits[2 * w + 1];
-      }
-      const unsigned long long varying = valid == FP_TILE ? (tor ^ tand) : ~0ull;
-#pragma unroll
-      for (int p = 0; p < KB; ++p) {
-        if ((varying >> (8 * p)) & 0xFFull) {
-#pragma unroll
-          for (int i = 0; i < FP_ITEMS; ++i) {
-            if (first + i < valid) {
-              const OK o           = FpKey<KB>::okey(key[i], xf);
-              const unsigned int b = (unsigned int)(bs >> (4 * i)) & 15u;
-              atomicAdd(&shist[(b * KB + p) * RADIX + ((unsigned int)(o >> (8 * p)) & 0xFFu)], 1u);
-            }
-          }
-        } else if (tid < FP_NB) {
-          const unsigned int c = fp_field(tlo, thi, tid);
-          if (c) atomicAdd(&shist[(tid * KB + p) * RADIX + ((unsigned int)(tor >> (8 * p)) & 0xFFu)], c);
-        }
-      }
     }
     // start of every destination's piece in the staged tile: inclusive prefix over the fields by one
     // multiplication (no field overflows: a tile holds fewer than 2^16 elements), minus the counts
@@ -587,13 +528,6 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
       }
     }
     __syncthreads();  // the tile's tables and staging buffers are free for the next tile
-  }
-  if (HIST) {
-    __syncthreads();
-    for (int i = tid; i < FP_NB * KB * RADIX; i += FP_THREADS) {
-      const unsigned int c = shist[i];
-      if (c) atomicAdd(&sent_hist[i], c);
-    }
   }
 }
 

@@ -26,6 +26,8 @@ struct RouteArgs {
   unsigned int n;
   int npass;
   int key_bytes;
+  uint4* zero_ptr;               // hist_kernel also clears this many 16-byte words (the look-back
+  unsigned long long zero_vecs;  // tables of the passes) while it waits for its shared-memory atomics
 };
 
 // Body of the scan-and-route step, run by one whole CTA of at least RADIX threads (threads beyond
@@ -168,6 +170,12 @@ hist_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int n, C
   __shared__ unsigned int sh[KB][RADIX];
   for (int i = threadIdx.x; i < KB * RADIX; i += HIST_THREADS) (&sh[0][0])[i] = 0;
   __syncthreads();
+
+  // the look-back tables of the passes start out empty: cleared here, where the memory pipe is
+  // mostly idle, instead of by a memset of their own in front of the sort
+  for (unsigned long long i = (unsigned long long)blockIdx.x * HIST_THREADS + threadIdx.x; i < route.zero_vecs;
+       i += (unsigned long long)gridDim.x * HIST_THREADS)
+    route.zero_ptr[i] = make_uint4(0u, 0u, 0u, 0u);
 
   constexpr int VEC = 16 / KB;  // keys per 128-bit load
   const bool aligned = (reinterpret_cast<uintptr_t>(keys) & 15u) == 0;

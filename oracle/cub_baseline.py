@@ -40,9 +40,11 @@ def available() -> bool:
     return os.path.exists(_SO)
 
 
-def time_sort(tile, argsort: bool, steps: int = 5, warmup: int = 2):
+def time_sort(tile, argsort: bool, steps: int = 5, warmup: int = 2, between=None):
     """Times the library sort on a device tensor (last axis = sort axis).  Returns (ms per step,
-    result tensor).  ``tile`` is a torch CUDA tensor of a supported dtype."""
+    result tensor).  ``tile`` is a torch CUDA tensor of a supported dtype.  ``between`` (a callable,
+    e.g. an L2 flush for inputs that fit the cache) runs before every timed step, outside the timed
+    interval; without it the steps are timed back to back."""
     import torch
 
     lib = _load()
@@ -69,6 +71,16 @@ def time_sort(tile, argsort: bool, steps: int = 5, warmup: int = 2):
         call()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if between is not None:
+        ms = 0.0
+        for _ in range(steps):
+            between()
+            e0.record()
+            call()
+            e1.record()
+            torch.cuda.synchronize()
+            ms += e0.elapsed_time(e1)
+        return ms / steps, (idx_out if argsort else keys_out)
     e0.record()
     for _ in range(steps):
         call()
