@@ -112,6 +112,10 @@ inline cudaError_t launch_sweeps(Ctrl* ctrl, unsigned int* lookback, unsigned in
   return cudaGetLastError();
 }
 
+#ifndef B2S_HIST_LANES
+#define B2S_HIST_LANES 1
+#endif
+
 template <int KB, int XF>
 inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsigned int n,
                                int64_t index_offset, unsigned char* ws, cudaStream_t stream, int idx32,
@@ -154,6 +158,16 @@ inline cudaError_t radix_1d_xf(const void* in, void* out, int64_t* idx_out, unsi
   } else {
     // digit histograms of all passes; the CTA that finishes last scans them and routes the passes
     prof::Scope ps(prof::K_HIST, stream);
+#if B2S_HIST_LANES
+    // one CTA per SM with a copy of the tables per lane; inputs too small to give every SM a few
+    // thousand keys take the single-table kernel
+    if (n >= (unsigned int)sms * HISTL_THREADS * 16) {
+      auto kern = hist_lanes_kernel<KB, XF>;
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)HistLanes<KB>::BYTES);
+      if (e != cudaSuccess) return e;
+      kern<<<sms, HISTL_THREADS, HistLanes<KB>::BYTES, stream>>>(static_cast<const K*>(in), n, ctrl, ra);
+    } else
+#endif
     hist_kernel<KB, XF><<<hgrid, HIST_THREADS, 0, stream>>>(static_cast<const K*>(in), n, ctrl, ra);
   }
   const SegGeom geo{n, lay.tiles, 1u, KB, nullptr};

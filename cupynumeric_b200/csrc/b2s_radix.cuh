@@ -215,6 +215,83 @@ hist_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int n, C
   scan_route_body(ctrl, route);
 }
 
+// The same histograms with one copy of every table per lane (KB <= 4) or per pair of lanes
+// (8-byte keys), laid out so that a lane's counters sit in the lane's own bank: an atomic
+// instruction of a warp then costs one shared-memory wavefront (at most two for 8-byte keys) instead
+// of the ~3 that 32 random digits cost in a single table - the single-table kernel is bound by
+// exactly those bank conflicts.  One CTA of 1024 threads per SM holds the copies (128 KB).
+constexpr int HISTL_THREADS = 1024;
+template <int KB> struct HistLanes {
+  static constexpr int COPIES   = KB <= 4 ? 32 : 16;
+  static constexpr size_t BYTES = (size_t)KB * RADIX * COPIES * sizeof(unsigned int);
+};
+
+template <int KB, int XF>
+__global__ void __launch_bounds__(HISTL_THREADS, 1)
+hist_lanes_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned int n, Ctrl* ctrl, RouteArgs route)
+{
+  using K = typename KeyOf<KB>::type;
+  constexpr int COPIES = HistLanes<KB>::COPIES;
+  extern __shared__ __align__(16) unsigned int histl_smem[];
+  unsigned int* sh = histl_smem;  // [(pass * RADIX + digit) * COPIES + copy]
+  for (int i = threadIdx.x; i < KB * RADIX * COPIES; i += HISTL_THREADS) sh[i] = 0;
+  for (unsigned long long i = (unsigned long long)blockIdx.x * HISTL_THREADS + threadIdx.x; i < route.zero_vecs;
+       i += (unsigned long long)gridDim.x * HISTL_THREADS)
+    route.zero_ptr[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+
+  constexpr int VEC = 16 / KB;  // keys per 128-bit load
+  constexpr int UNROLL = 4;     // loads in flight per thread
+  const unsigned int copy    = threadIdx.x & (COPIES - 1);
+  const bool aligned         = (reinterpret_cast<uintptr_t>(keys) & 15u) == 0;
+  const unsigned int nvec    = aligned ? n / VEC : 0;
+  const unsigned int gthread = blockIdx.x * HISTL_THREADS + threadIdx.x;
+  const unsigned int gstride = gridDim.x * HISTL_THREADS;
+  const uint4* vkeys         = reinterpret_cast<const uint4*>(keys);
+  auto add = [&](K raw) {
+    const auto k = to_ordered<KB, XF>(raw);
+#pragma unroll
+    for (int p = 0; p < KB; ++p) atomicAdd(&sh[(p * RADIX + ((unsigned int)(k >> (8 * p)) & 0xFFu)) * COPIES + copy], 1u);
+  };
+  unsigned int v = gthread;
+  for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
+    uint4 q[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) q[u] = __ldg(vkeys + v + u * gstride);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      alignas(16) K tmp[VEC];
+      *reinterpret_cast<uint4*>(tmp) = q[u];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) add(tmp[j]);
+    }
+  }
+  for (; v < nvec; v += gstride) {
+    alignas(16) K tmp[VEC];
+    *reinterpret_cast<uint4*>(tmp) = __ldg(vkeys + v);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) add(tmp[j]);
+  }
+  for (unsigned int i = nvec * VEC + gthread; i < n; i += gstride) add(keys[i]);
+  __syncthreads();
+  // sum of the copies of every counter; thread t starts at copy t so that the threads of a warp
+  // read different banks
+  for (int i = threadIdx.x; i < KB * RADIX; i += HISTL_THREADS) {
+    unsigned int c = 0;
+#pragma unroll 8
+    for (int j = 0; j < COPIES; ++j) c += sh[i * COPIES + ((j + threadIdx.x) & (COPIES - 1))];
+    if (c) atomicAdd(&ctrl->hist[0][0] + i, c);
+  }
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(&ctrl->hist_done, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  scan_route_body(ctrl, route);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Per-segment variants of kernels 1 and 2 for segments too long for the on-chip sort: one CTA
 // counts one chunk of one segment; a second kernel turns each 256-bin histogram into bases.
