@@ -60,11 +60,39 @@ select_pass_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned l
   const unsigned long long prefix = st->prefix;
   // bits above the digit of this pass
   const unsigned long long himask = pass == 0 ? 0ull : (~0ull << (shift + 8)) & (KB == 8 ? ~0ull : ((1ull << (8 * KB)) - 1));
-  const unsigned long long stride = (unsigned long long)gridDim.x * SEL_THREADS;
-  for (unsigned long long i = (unsigned long long)blockIdx.x * SEL_THREADS + tid; i < n; i += stride) {
-    const unsigned long long o = (unsigned long long)to_ordered_rt<KB>(keys[i], xf);
+  auto look = [&](K raw) {
+    const unsigned long long o = (unsigned long long)to_ordered_rt<KB>(raw, xf);
     if ((o & himask) == prefix) atomicAdd(&sh[(unsigned int)(o >> shift) & 0xFFu], 1u);
+  };
+  // 16-byte loads, four in flight per thread: after the first pass almost no key matches the prefix
+  // and the pass is a plain read of the input
+  constexpr int VEC    = 16 / KB;
+  constexpr int UNROLL = 4;
+  const bool aligned   = (reinterpret_cast<uintptr_t>(keys) & 15u) == 0;
+  const unsigned long long nvec    = aligned ? n / VEC : 0;
+  const unsigned long long gthread = (unsigned long long)blockIdx.x * SEL_THREADS + tid;
+  const unsigned long long stride  = (unsigned long long)gridDim.x * SEL_THREADS;
+  const uint4* vkeys               = reinterpret_cast<const uint4*>(keys);
+  unsigned long long v             = gthread;
+  for (; v + (UNROLL - 1) * stride < nvec; v += UNROLL * stride) {
+    uint4 q[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) q[u] = __ldg(vkeys + v + u * stride);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      alignas(16) K tmp[VEC];
+      *reinterpret_cast<uint4*>(tmp) = q[u];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) look(tmp[j]);
+    }
   }
+  for (; v < nvec; v += stride) {
+    alignas(16) K tmp[VEC];
+    *reinterpret_cast<uint4*>(tmp) = __ldg(vkeys + v);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) look(tmp[j]);
+  }
+  for (unsigned long long i = nvec * VEC + gthread; i < n; i += stride) look(keys[i]);
   __syncthreads();
   if (tid < RADIX && sh[tid]) atomicAdd(&st->hist[tid], sh[tid]);
   __threadfence();
@@ -114,49 +142,97 @@ select_pass_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned l
 }
 
 // Three blocks: [keys below the pivot][keys equal to it][keys above it]; the order inside a block is
-// whatever the CTAs' reservations make it (a partition promises no more).
+// whatever the CTAs' reservations make it (a partition promises no more).  Every thread counts its
+// elements per block in one packed word (three 16-bit fields), one scan of those words over the CTA
+// gives every element its place in the CTA's three pieces, the pieces are put together in shared
+// memory and written out as three runs of consecutive elements.
+constexpr int P3_ITEMS = 8;
+constexpr int P3_TILE  = SEL_THREADS * P3_ITEMS;
+
 template <int KB>
-__global__ void __launch_bounds__(SEL_THREADS)
+__global__ void __launch_bounds__(SEL_THREADS, 3)
 partition3_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned long long n, int xf, SelectState* st,
                   typename KeyOf<KB>::type* __restrict__ out_keys, int64_t* __restrict__ out_idx, int64_t index_offset)
 {
-  using K = typename KeyOf<KB>::type;
-  constexpr int ITEMS = 8;
-  __shared__ unsigned int cnt[3], base[3];
-  const int tid = threadIdx.x, lane = tid & 31;
-  const unsigned long long pivot = st->prefix;
-  const unsigned long long start[3] = {0ull, st->below, st->below + st->equal};
-  const unsigned long long tile0 = (unsigned long long)blockIdx.x * (SEL_THREADS * ITEMS);
-  if (tid < 3) cnt[tid] = 0;
-  __syncthreads();
-  K key[ITEMS];
-  unsigned int cls[ITEMS], rank[ITEMS];
+  using K  = typename KeyOf<KB>::type;
+  using OK = typename KeyOf<(KB <= 4 ? 4 : 8)>::type;  // comparisons of short keys stay 32-bit
+  constexpr int WARPS = SEL_THREADS / 32;
+  constexpr unsigned int F1 = 1u << 10, F2 = 1u << 20;  // a warp holds at most 256 elements: 10-bit fields
+  __shared__ K skey[P3_TILE];
+  __shared__ unsigned short ssrc[P3_TILE];     // where in the tile the staged element came from
+  __shared__ unsigned int wtot[WARPS];
+  __shared__ unsigned int base[3];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const OK pivot                 = (OK)st->prefix;
+  const unsigned long long tile0 = (unsigned long long)blockIdx.x * P3_TILE;
+  const unsigned int valid       = (unsigned int)min((unsigned long long)P3_TILE, n - tile0);
+  const K* src                   = keys + tile0;
+  K key[P3_ITEMS];
+  unsigned int incs[P3_ITEMS];  // 0: no element; else the element's class as its counter increment
+  unsigned int cnt = 0;
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    const unsigned long long e = tile0 + (unsigned long long)i * SEL_THREADS + tid;
-    cls[i] = 3;
-    if (e < n) {
-      key[i]                     = keys[e];
-      const unsigned long long o = (unsigned long long)to_ordered_rt<KB>(key[i], xf);
-      cls[i]                     = o < pivot ? 0u : (o == pivot ? 1u : 2u);
+  for (int i = 0; i < P3_ITEMS; ++i) {
+    const unsigned int e = i * SEL_THREADS + tid;
+    incs[i]              = 0;
+    if (e < valid) {
+      key[i]     = src[e];
+      const OK o = (OK)to_ordered_rt<KB>(key[i], xf);
+      incs[i]    = o < pivot ? 1u : (o == pivot ? F1 : F2);
+      cnt += incs[i];
     }
-    // one shared-memory atomic per class and warp
-    const unsigned int peers = __match_any_sync(0xFFFFFFFFu, cls[i]);
-    unsigned int first       = 0;
-    if (cls[i] < 3 && lane == __ffs(peers) - 1) first = atomicAdd(&cnt[cls[i]], (unsigned int)__popc(peers));
-    first   = __shfl_sync(0xFFFFFFFFu, first, __ffs(peers) - 1);
-    rank[i] = first + __popc(peers & lanemask_lt());
   }
-  __syncthreads();
-  if (tid < 3) base[tid] = atomicAdd(&st->cursor[tid], cnt[tid]);
-  __syncthreads();
+  // exclusive prefix of the packed counts: inside the warp on the packed word, over the warps on
+  // the three unpacked totals
+  unsigned int incl = cnt;
 #pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    if (cls[i] < 3) {
-      const unsigned long long at = start[cls[i]] + base[cls[i]] + rank[i];
-      if (out_keys != nullptr) out_keys[at] = key[i];
-      if (out_idx != nullptr) out_idx[at] = index_offset + (int64_t)(tile0 + (unsigned long long)i * SEL_THREADS + tid);
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned int t = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) wtot[warp] = incl;
+  __syncthreads();
+  unsigned int b0 = 0, b1 = 0, b2 = 0, t0 = 0, t1 = 0, t2 = 0;  // elements of lower warps / of the CTA, per class
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) {
+    const unsigned int t = wtot[w];
+    const unsigned int c0 = t & 0x3FFu, c1 = (t >> 10) & 0x3FFu, c2 = t >> 20;
+    if (w < warp) {
+      b0 += c0;
+      b1 += c1;
+      b2 += c2;
     }
+    t0 += c0;
+    t1 += c1;
+    t2 += c2;
+  }
+  // the reservation travels to L2 and back while the tile is being staged
+  unsigned int reserved = 0;
+  if (tid < 3) {
+    const unsigned int mine = tid == 0 ? t0 : (tid == 1 ? t1 : t2);
+    if (mine) reserved = atomicAdd(&st->cursor[tid], mine);
+  }
+  // my first place in each of the CTA's three pieces (pieces start at 0, t0, t0 + t1)
+  const unsigned int excl = incl - cnt;
+  unsigned int p0 = b0 + (excl & 0x3FFu), p1 = t0 + b1 + ((excl >> 10) & 0x3FFu), p2 = t0 + t1 + b2 + (excl >> 20);
+  const bool want_idx = out_idx != nullptr;
+#pragma unroll
+  for (int i = 0; i < P3_ITEMS; ++i) {
+    if (incs[i]) {
+      unsigned int p;
+      if (incs[i] == 1u) p = p0++; else if (incs[i] == F1) p = p1++; else p = p2++;
+      skey[p] = key[i];
+      if (want_idx) ssrc[p] = (unsigned short)(i * SEL_THREADS + tid);
+    }
+  }
+  if (tid < 3) base[tid] = reserved;
+  __syncthreads();
+  // the staged tile goes out as three runs of consecutive elements
+  const unsigned long long below = st->below, equal = st->equal;
+  const unsigned long long d0 = base[0], d1 = below + base[1] - t0, d2 = below + equal + base[2] - (t0 + t1);
+  for (unsigned int p = tid; p < valid; p += SEL_THREADS) {
+    const unsigned long long at = (p < t0 ? d0 : (p < t0 + t1 ? d1 : d2)) + p;
+    if (out_keys != nullptr) out_keys[at] = skey[p];
+    if (want_idx) out_idx[at] = index_offset + (int64_t)(tile0 + ssrc[p]);
   }
 }
 
@@ -180,7 +256,7 @@ static cudaError_t run_partition(const void* keys_in, void* keys_out, int64_t* i
   }
   {
     prof::Scope ps(prof::K_FIXUP, stream);
-    const unsigned int tiles = (unsigned int)((n + SEL_THREADS * 8 - 1) / (SEL_THREADS * 8));
+    const unsigned int tiles = (unsigned int)((n + P3_TILE - 1) / P3_TILE);
     partition3_kernel<KB><<<tiles, SEL_THREADS, 0, stream>>>(static_cast<const K*>(keys_in), n, xf, st, static_cast<K*>(keys_out),
                                                              idx_out, index_offset);
   }

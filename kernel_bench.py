@@ -2,6 +2,7 @@
 
     python kernel_bench.py merge --dtype int64 --runs 8 --log2 27 [--payload]
     python kernel_bench.py sort  --dtype float32 --log2 28 [--argsort] [--segment L]
+    python kernel_bench.py select --dtype float32 --log2 28 [--argsort]      (partition by selection, kth = n/2)
 
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
         kernel_bench.py dist --dtype float32 --log2 27 [--argsort]
@@ -105,6 +106,40 @@ def bench_sort(args) -> None:
     ms = a.elapsed_time(b) / args.iters
     print(f"sort {args.dtype} n=2^{args.log2} segment={args.segment or n} argsort={args.argsort}: {ms:.3f} ms "
           f"-> {n / ms / 1e6:.1f} Gkeys/s; {_report(lib, args.iters)}")
+    lib.b2s_profile_enable(0)
+
+
+def bench_select(args) -> None:
+    """b2s_partition_1d (radix select + three-block partition) at kth = n / 2."""
+    lib = _lib.lib()
+    dtype = getattr(torch, args.dtype)
+    n = 1 << args.log2
+    x = _random(dtype, n)
+    out = torch.empty(n, dtype=torch.int64 if args.argsort else dtype, device="cuda")
+    need = ctypes.c_size_t(0)
+    _lib.check(lib.b2s_partition_workspace_bytes(ctypes.byref(need)), "b2s_partition_workspace_bytes")
+    ws = torch.empty(max(need.value, 256), dtype=torch.uint8, device="cuda")
+    code = _lib.DTYPE_CODE[np.dtype(args.dtype)]
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        _lib.check(lib.b2s_partition_1d(code, x.data_ptr(), None if args.argsort else out.data_ptr(),
+                                        out.data_ptr() if args.argsort else None, n, n // 2, 0, ws.data_ptr(), ws.numel(), stream),
+                   "b2s_partition_1d")
+
+    for _ in range(args.warmup):
+        call()
+    torch.cuda.synchronize()
+    lib.b2s_profile_enable(1)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.iters):
+        call()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.iters
+    print(f"select {args.dtype} n=2^{args.log2} kth=n/2 argsort={args.argsort}: {ms:.3f} ms -> {n / ms / 1e6:.1f} Gkeys/s; "
+          f"{_report(lib, args.iters)}")
     lib.b2s_profile_enable(0)
 
 
@@ -228,6 +263,10 @@ def main() -> None:
     s.add_argument("--log2", type=int, default=28)
     s.add_argument("--argsort", action="store_true")
     s.add_argument("--segment", type=int, default=0)
+    q = sub.add_parser("select")
+    q.add_argument("--dtype", default="float32")
+    q.add_argument("--log2", type=int, default=28)
+    q.add_argument("--argsort", action="store_true")
     d = sub.add_parser("dist")
     d.add_argument("--dtype", default="float32")
     d.add_argument("--log2", type=int, default=27)
@@ -237,7 +276,7 @@ def main() -> None:
     t.add_argument("--dtype", default="float32")
     t.add_argument("--log2", type=int, default=24)
     t.add_argument("--argsort", action="store_true")
-    for p in (m, s, d, t):
+    for p in (m, s, q, d, t):
         p.add_argument("--iters", type=int, default=5)
         p.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
@@ -248,7 +287,7 @@ def main() -> None:
         bench_dist(args)
         return
     torch.cuda.set_device(0)
-    {"merge": bench_merge, "sort": bench_sort, "dist-threads": bench_dist_threads}[args.what](args)
+    {"merge": bench_merge, "sort": bench_sort, "select": bench_select, "dist-threads": bench_dist_threads}[args.what](args)
 
 
 if __name__ == "__main__":
