@@ -38,6 +38,21 @@ def test_sort_and_argsort_1d_all_sizes(cuda_device, dtype, flavour):
         assert np.array_equal(got_i, want_i), f"argsort {np.dtype(dtype)} n={n}"
 
 
+@pytest.mark.parametrize("dtype", [np.uint8, np.int16, np.float16, np.int32, np.float32, np.int64, np.float64])
+def test_more_tiles_than_the_gpu_holds_at_once(cuda_device, dtype):
+    """2^23 + 5 keys per key width: over a thousand tiles per pass, several waves of CTAs, so the
+    chained look-back crosses CTAs that are not resident together; the histogram kernel with a
+    copy of the tables per lane runs here too.  Bit for bit against the oracle."""
+    rng = np.random.default_rng(2323)
+    n = (1 << 23) + 5
+    a = random_keys(rng, dtype, n, "full")
+    want_k, want_i = expected(a, n, True, index_offset=3)
+    got_k, _ = cabi_local_sort(a, n, False)
+    assert_bit_equal(got_k, want_k, f"sort {np.dtype(dtype)}")
+    _, got_i = cabi_local_sort(a, n, True, index_offset=3)
+    assert np.array_equal(got_i, want_i), f"argsort {np.dtype(dtype)}"
+
+
 @pytest.mark.parametrize("dtype", [np.int32, np.float32, np.uint64, np.float64, np.int8, np.float16])
 def test_inplace_and_keys_with_indices(cuda_device, dtype):
     rng = np.random.default_rng(99)
