@@ -248,10 +248,22 @@ hist_lanes_kernel(const typename KeyOf<KB>::type* __restrict__ keys, unsigned in
   const unsigned int gthread = blockIdx.x * HISTL_THREADS + threadIdx.x;
   const unsigned int gstride = gridDim.x * HISTL_THREADS;
   const uint4* vkeys         = reinterpret_cast<const uint4*>(keys);
+  // Byte offset of a counter: table p starts at p * TABLE, a digit's copies at digit * ROW, mine at
+  // copy * 4 (below ROW, so it can be OR-ed in): a shift, a logic operation and an add per digit,
+  // then a reduction that returns nothing.
+  constexpr unsigned int ROW = COPIES * 4, TABLE = RADIX * ROW;
+  constexpr int ROW_LOG2     = COPIES == 32 ? 7 : 6;
+  const unsigned int window  = (unsigned int)__cvta_generic_to_shared(sh);
+  const unsigned int mine    = copy * 4u;
   auto add = [&](K raw) {
     const auto k = to_ordered<KB, XF>(raw);
 #pragma unroll
-    for (int p = 0; p < KB; ++p) atomicAdd(&sh[(p * RADIX + ((unsigned int)(k >> (8 * p)) & 0xFFu)) * COPIES + copy], 1u);
+    for (int p = 0; p < KB; ++p) {
+      const int sh_by         = 8 * p - ROW_LOG2;  // digit << ROW_LOG2, taken straight from the key
+      const unsigned int slot = (unsigned int)(sh_by >= 0 ? (k >> (sh_by >= 0 ? sh_by : 0)) : (k << (sh_by < 0 ? -sh_by : 0))) &
+                                (0xFFu << ROW_LOG2);
+      asm volatile("red.shared.add.u32 [%0], 1;" ::"r"((slot | mine) + (window + p * TABLE)) : "memory");
+    }
   };
   unsigned int v = gthread;
   for (; v + (UNROLL - 1) * gstride < nvec; v += UNROLL * gstride) {
