@@ -518,8 +518,8 @@ struct PhaseTrace {
   explicit PhaseTrace(int rank)
     : on(std::getenv("B2S_DIST_TRACE") != nullptr && (rank == 0 || std::getenv("B2S_DIST_TRACE")[0] == 'a')), rk(rank),
       t0(std::chrono::steady_clock::now()) {}
-  // B2S_DIST_TRACE=sync (rank 0) / async... : "s" as second character waits for the stream first, so
-  // that the figures are device times per phase instead of enqueue times
+  // "s" as the second character of the value waits for the stream first, so that the figures are
+  // device times per phase instead of enqueue times
   void mark(const char* what, cudaStream_t stream = nullptr)
   {
     if (!on) return;
