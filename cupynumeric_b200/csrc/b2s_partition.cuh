@@ -368,14 +368,15 @@ template <int KB, int PAYB> struct FpSmem {
   static constexpr size_t OFF_DKEY  = OFF_GOFF + FP_NB * 8;
   static constexpr size_t OFF_DPAY  = OFF_DKEY + FP_NB * 8;
   static constexpr size_t OFF_BAR   = OFF_DPAY + FP_NB * 8;
-  static constexpr size_t BYTES     = OFF_BAR + 8;
+  static constexpr size_t OFF_POS   = (OFF_BAR + 8 + 15) / 16 * 16;    // FP_NB x FP_THREADS next places, one row per destination
+  static constexpr size_t BYTES     = OFF_POS + (size_t)FP_NB * FP_THREADS * 4;
 };
 
 // Stable partition of tiles into the destinations' receive buffers (see the vote-based kernel
 // of the same role for the contract).  CTA c takes tiles c, c + gridDim.x, ...; launched with one
 // CTA per tile.
 template <int KB, int PAYB>
-__global__ void __launch_bounds__(FP_THREADS)
+__global__ void __launch_bounds__(FP_THREADS, 4)
 part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long long n, int xf,
                          const LocalSplitter* __restrict__ split, const unsigned long long* __restrict__ tile_off,
                          const __grid_constant__ FpDst dst, long long global_offset, long long pay_base,
@@ -394,6 +395,7 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
   void** dkey              = reinterpret_cast<void**>(smem + S::OFF_DKEY);
   void** dpay              = reinterpret_cast<void**>(smem + S::OFF_DPAY);
   uint64_t* bar            = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  unsigned int* spos       = reinterpret_cast<unsigned int*>(smem + S::OFF_POS);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long long ntiles = (n + FP_TILE - 1) / FP_TILE;
@@ -492,18 +494,26 @@ part_scatter_fast_kernel(const typename FpKey<KB>::Raw* __restrict__ keys, long 
       for (int b = 0; b < FP_NB; ++b) bstart[b] = fp_field(inc_lo - tlo, inc_hi - thi, b);
       bstart[FP_NB] = (unsigned int)valid;
     }
-    // stage: position = start of the destination's piece + elements of lower threads + my earlier ones
+    // stage: position = start of the destination's piece + elements of lower threads + my earlier
+    // ones.  The thread's next place per destination lives in its own column of a small table in
+    // shared memory (column = thread = bank: no conflicts, and nobody else touches it): a load, an add
+    // and a store per element instead of field arithmetic on the packed 64-bit words.
+    unsigned int* my_pos = spos + tid;
+#pragma unroll
+    for (int b = 0; b < FP_NB; ++b) my_pos[b * FP_THREADS] = fp_field(plo, phi, b);
+    const long long g0 = global_offset + base + first;
+    const uint32_t g32 = (uint32_t)(g0 - pay_base);
 #pragma unroll
     for (int i = 0; i < FP_ITEMS; ++i) {
       const unsigned int b = (unsigned int)(bs >> (4 * i)) & 15u;
       if (first + i < valid) {
-        const unsigned int p = fp_field(plo, phi, b);
+        unsigned int* q      = my_pos + b * FP_THREADS;
+        const unsigned int p = *q;
+        *q                   = p + 1;
         skeys[p]             = key[i];
-        const long long g    = global_offset + base + first + i;
-        if (PAYB == 4) reinterpret_cast<uint32_t*>(spay)[p] = (uint32_t)(g - pay_base);
-        if (PAYB == 8) reinterpret_cast<int64_t*>(spay)[p] = (int64_t)g;
+        if (PAYB == 4) reinterpret_cast<uint32_t*>(spay)[p] = g32 + (uint32_t)i;
+        if (PAYB == 8) reinterpret_cast<int64_t*>(spay)[p] = (int64_t)(g0 + i);
       }
-      fp_count(plo, phi, b, true);
     }
     __syncthreads();
     // copy-out, one destination after the other: a warp stores groups of 32 consecutive elements
